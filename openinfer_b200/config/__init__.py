@@ -10,12 +10,13 @@ from .base import (
     resolve_architecture,
     unregister_architecture,
 )
+from .bubalix import BubalixConfig
 from .delunex import DelunexConfig
 from .pilonex import PilonexConfig
 from .qwen3 import Qwen3Config
 
 __all__ = [
-    "ArchitectureEntry", "ConfigError", "DelunexConfig", "ModelConfig", "PilonexConfig", "Qwen3Config", "known_architectures",
+    "ArchitectureEntry", "BubalixConfig", "ConfigError", "DelunexConfig", "ModelConfig", "PilonexConfig", "Qwen3Config", "known_architectures",
     "load_config", "read_config_json", "register_architecture", "resolve_architecture",
     "unregister_architecture",
 ]

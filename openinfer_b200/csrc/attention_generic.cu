@@ -9,7 +9,13 @@
 // batch, so a row's result does not depend on how the batch was cut.
 //
 // This is the kernel of the true 32-bit path and of every shape the tuned kernels refuse.
+//
+// Score modifiers (OiScoreMods, all optional): the score of a query at position p is multiplied by
+// 1 + coef * ln(floor((p + 1) / every) + 1); then capped, s <- cap * tanh(s / cap); then slope_h * (i - j) is taken off;
+// and the softmax's denominator gets one more term exp(sink_h), which has no key and no value (it enters as the state
+// the online softmax starts from: maximum sink_h, sum 1, nothing accumulated).
 #include "common.cuh"
+#include "oi_api.h"
 
 #define ATTN_MAX_HD 512   // heads of more than 256 elements (a wide latent read as keys and values) get a second instance
 
@@ -42,7 +48,7 @@ __global__ void attention_generic_kernel(
     const T* __restrict__ q, int q_row_stride, T* __restrict__ out, int out_row_stride,
     const T* __restrict__ k_cache, const T* __restrict__ v_cache, long long page_stride, int page_size,
     const int* __restrict__ block_table, int bt_stride, const int* __restrict__ token_req,
-    const int* __restrict__ positions, int nq, int nkv, int hd, float scale, int window, int tokens) {
+    const int* __restrict__ positions, int nq, int nkv, int hd, float scale, int window, int tokens, OiScoreMods mods) {
   pdl_start();
   __shared__ float q_sh[kWarps][kMaxHd];
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -67,6 +73,10 @@ __global__ void attention_generic_kernel(
 #pragma unroll
   for (int r = 0; r < kAccs; ++r) acc[r] = 0.f;
   float m = -INFINITY, l = 0.f;
+  if (mods.sinks) { m = mods.sinks[head]; l = 1.f; }
+  if (mods.qt_every > 0) scale *= 1.f + mods.qt_coef * logf((float)((pos + 1) / mods.qt_every) + 1.f);
+  const float slope = mods.slopes ? mods.slopes[head] : 0.f;
+  const float cap = mods.softcap, inv_cap = cap > 0.f ? 1.f / cap : 0.f;
 
   for (int base = first; base <= pos; base += 32) {
     const int j = base + lane;
@@ -82,6 +92,8 @@ __global__ void attention_generic_kernel(
         for (int e = 0; e < VN; ++e) dot += q_sh[warp][d + e] * kv[e];
       }
       s = dot * scale;
+      if (cap > 0.f) s = cap * tanhf(s * inv_cap);
+      s -= slope * (float)(pos - j);
     }
     const float m_new = fmaxf(m, warp_max(s));
     const float p = (j <= pos) ? expf(s - m_new) : 0.f;
@@ -116,20 +128,22 @@ OI_API int oi_attention_generic(const void* q, int q_row_stride, void* out, int 
                                 const void* k_cache, const void* v_cache, long long page_stride,
                                 int page_size, const int* block_table, int bt_stride,
                                 const int* token_req, const int* positions, int tokens, int nq, int nkv,
-                                int hd, float scale, int window, void* stream) {
+                                int hd, float scale, int window, const OiScoreMods* mods_in, void* stream) {
   OI_REQUIRE(tokens >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention: bad head counts nq=%d nkv=%d", nq, nkv);
   OI_REQUIRE(hd > 0 && hd % 8 == 0 && hd <= ATTN_MAX_HD,
              "attention: head_dim %d unsupported (multiples of 8 up to %d)", hd, ATTN_MAX_HD);
   OI_REQUIRE(q_row_stride % 8 == 0 && page_stride % 8 == 0, "attention: strides must be multiples of 8 elements");
   OI_REQUIRE(page_size > 0, "attention: page_size %d", page_size);
   if (tokens == 0) return OI_OK;
+  OiScoreMods mods = {};
+  if (mods_in) mods = *mods_in;
   constexpr int kWarps = 4;
   dim3 grid(tokens, (nq + kWarps - 1) / kWarps);
   cudaStream_t s = (cudaStream_t)stream;
 #define OI_ATTN_GENERIC(T, MAXHD)                                                                                   \
   oi_launch(attention_generic_kernel<T, kWarps, MAXHD>, grid, kWarps * 32, 0, s, (const T*)q, q_row_stride, (T*)out,  \
             out_row_stride, (const T*)k_cache, (const T*)v_cache, page_stride, page_size, block_table, bt_stride,    \
-            token_req, positions, nq, nkv, hd, scale, window, tokens)
+            token_req, positions, nq, nkv, hd, scale, window, tokens, mods)
   if (dtype == OI_F32) {
     if (hd <= 256) OI_ATTN_GENERIC(float, 256); else OI_ATTN_GENERIC(float, 512);
   } else if (dtype == OI_BF16) {

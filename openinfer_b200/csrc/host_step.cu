@@ -200,7 +200,7 @@ OI_API int oi_attention_layer(const OiAttnStep* s, const OiAttnLayer* l, void* s
   if (!s->tensor_core)
     return oi_attention_generic(l->qkv, l->q_row_stride, l->out, l->out_row_stride, l->dtype, l->k_cache, l->v_cache,
                                 s->page_stride, s->page_size, s->block_table, s->bt_stride, s->token_req, s->positions,
-                                tokens, l->nq, l->nkv, l->hd, l->scale, l->window, stream);
+                                tokens, l->nq, l->nkv, l->hd, l->scale, l->window, &l->mods, stream);
   if (fused) {
     OI_REQUIRE(s->num_tile_items == 0 && s->num_decode_items > 0, "attention_layer: the fused rotation needs a step of single tokens");
     return oi_attention_decode_rope(l->qkv, l->q_row_stride, l->out, l->out_row_stride, l->k_cache, l->v_cache, s->page_stride,

@@ -173,14 +173,14 @@ __global__ void moe_group_kernel(const int* __restrict__ ids, int pairs, int E, 
 }
 
 // out rows of one tile: C[i, n] = sum_k A[src(i), k] * W_e[n, k] (k ascending), i over the tile's sorted places.
-// kGlu: W_e holds N gate rows and then N up rows; the result is g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit),
-// u' = clamp(u, -limit, limit). a_div: the source row of place i is sorted[i] / a_div (a_div 0: the place itself).
+// kGlu: W_e holds N gate rows and then N up rows; the result is the gated activation `act` of the two sums (glu_act:
+// act(g) * u, or with OI_ACT_SWIGLU_CLAMP g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit)). a_div: the source row of place i is sorted[i] / a_div (a_div 0: the place itself).
 // scatter: the result of place i goes to row sorted[i] (else to row i).
 template <typename T, typename TO, bool kGlu>
 __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, long long lda, int a_div, const T* __restrict__ Wt,
                                                        long long w_expert_stride, TO* __restrict__ out, long long ld_out, int scatter,
                                                        const int* __restrict__ sorted, const int* __restrict__ tile_info,
-                                                       int max_tiles, int N, int K, float limit) {
+                                                       int max_tiles, int N, int K, float limit, int act) {
   pdl_wait();    // no early trigger: waiting blocks of the next kernel would share the SMs with this product
   const int tile = blockIdx.x;
   if (tile >= tile_info[3 * max_tiles]) return;
@@ -274,8 +274,7 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
       if (n >= N) continue;
       float v = acc[i][j];
       if (kGlu) {
-        const float g = fminf(v, limit), u = fminf(fmaxf(accu[i][j], -limit), limit);
-        v = g / (1.f + expf(-1.702f * g)) * (u + 1.f);
+        v = glu_act<false>(v, accu[i][j], act, limit);
       }
       out[row * ld_out + n] = from_f32<TO>(v);
     }
@@ -295,7 +294,7 @@ template <typename TO, bool kGlu>
 __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const bf16* __restrict__ A, long long lda, int a_div, const bf16* __restrict__ Wt,
                                                            long long w_expert_stride, TO* __restrict__ out, long long ld_out,
                                                            int scatter, const int* __restrict__ sorted,
-                                                           const int* __restrict__ tile_info, int max_tiles, int N, int K, float limit) {
+                                                           const int* __restrict__ tile_info, int max_tiles, int N, int K, float limit, int act) {
   pdl_wait();
   const int tile = blockIdx.x;
   if (tile >= tile_info[3 * max_tiles]) return;
@@ -365,8 +364,7 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const bf16* __restric
       const size_t row = scatter ? (size_t)sorted[place] : (size_t)place;
       float v = acc[j][c];
       if (kGlu) {
-        const float gc = fminf(v, limit), uc = fminf(fmaxf(accu[j][c], -limit), limit);
-        v = gc / (1.f + expf(-1.702f * gc)) * (uc + 1.f);
+        v = glu_act<false>(v, accu[j][c], act, limit);
       }
       out[row * ld_out + n] = from_f32<TO>(v);
     }
@@ -378,7 +376,7 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const bf16* __restric
 template <typename T, typename TO, bool kGlu>
 __global__ void __launch_bounds__(128) moe_gemv_kernel(const T* __restrict__ A, long long lda, int a_div, const T* __restrict__ Wt,
                                                        long long w_expert_stride, TO* __restrict__ out, long long ld_out,
-                                                       const int* __restrict__ ids, int N, int K, float limit) {
+                                                       const int* __restrict__ ids, int N, int K, float limit, int act) {
   pdl_wait();    // no early trigger: waiting blocks of the next kernel would share the SMs with this product
   extern __shared__ __align__(16) float xs[];
   constexpr int kVec = 16 / (int)sizeof(T), kRows = 16;
@@ -414,22 +412,22 @@ __global__ void __launch_bounds__(128) moe_gemv_kernel(const T* __restrict__ A, 
     if (lane == 0) {
       float v = g;
       if (kGlu) {
-        const float gc = fminf(g, limit), uc = fminf(fmaxf(u, -limit), limit);
-        v = gc / (1.f + expf(-1.702f * gc)) * (uc + 1.f);
+        v = glu_act<false>(g, u, act, limit);
       }
       out[(size_t)p * ld_out + n] = from_f32<TO>(v);
     }
   }
 }
 
+// add (or null): a float32 term per output number that every row gets beside its experts' sum (an expert all rows share)
 __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restrict__ y, const float* __restrict__ wts, int top, int W,
-                                   size_t n) {
+                                   size_t n, const float* __restrict__ add) {
   pdl_start();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (size_t)gridDim.x * blockDim.x) {
     const size_t t = i / W, c = i - t * W;
     float acc = 0.f;
     for (int j = 0; j < top; ++j) acc += wts[t * top + j] * y[(t * top + j) * W + c];
-    out[i] = acc;
+    out[i] = add ? acc + add[i] : acc;
   }
 }
 
@@ -464,11 +462,45 @@ OI_API int oi_moe_route(const void* x, int dtype, long long ldx, const void* w_r
   return OI_OK;
 }
 
-// act [rows * top, F] (scratch, `dtype`), y [rows * top, W] float32 (scratch), out [rows, W] float32.
+namespace {
+// Routing without a router: row t uses the experts table[token_ids[t], :], each with the same weight.
+__global__ void moe_table_kernel(const int* __restrict__ token_ids, const int* __restrict__ table, int rows, int vocab, int E, int top,
+                                 float weight, int* __restrict__ ids, float* __restrict__ wts) {
+  pdl_start();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= rows * top) return;
+  int tok = token_ids[i / top];
+  tok = tok < 0 ? 0 : (tok >= vocab ? vocab - 1 : tok);
+  int e = table[(size_t)tok * top + i % top];
+  ids[i] = e < 0 ? 0 : (e >= E ? E - 1 : e);
+  wts[i] = weight;
+}
+}  // namespace
+
+// The same outputs as oi_moe_route for a layer whose experts are chosen by the token id: table [vocab, top] int32 (the
+// entries of a row differ), every chosen expert weighted 1 / top.
+OI_API int oi_moe_route_table(const int* token_ids, const int* table, int rows, int vocab, int E, int top, int* ids, float* wts,
+                              int* sorted, int* tile_info, void* stream) {
+  OI_REQUIRE(rows >= 0 && vocab > 0 && E > 0 && top > 0 && top <= E && top <= kMaxTop, "moe_route_table: bad sizes experts=%d top=%d (at most %d)",
+             E, top, kMaxTop);
+  OI_REQUIRE(E <= 4096, "moe_route_table: %d experts, at most 4096", E);
+  if (rows == 0) return OI_OK;
+  cudaStream_t s = (cudaStream_t)stream;
+  const int pairs = rows * top;
+  oi_launch(moe_table_kernel, (pairs + 127) / 128, 128, 0, s, token_ids, table, rows, vocab, E, top, 1.f / (float)top, ids, wts);
+  OI_CHECK_LAUNCH();
+  if (oi_moe_small(pairs, E)) return OI_OK;
+  oi_launch(moe_group_kernel, E, 256, (size_t)(E + 8) * sizeof(int), s, (const int*)ids, pairs, E, sorted, tile_info, oi_moe_max_tiles(pairs, E));
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+// act [rows * top, F] (scratch, `dtype`), y [rows * top, W] float32 (scratch), out [rows, W] float32; add [rows, W] float32
+// or null: added to the weighted sum (out may be add itself).
 // w_gate_up [E, 2 F, W] (F gate rows, then F up rows), w_down [E, W, F], both in `dtype`.
 OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w_gate_up, const void* w_down, int rows, int W, int F,
-                          int E, int top, float limit, const int* ids, const int* sorted, const int* tile_info, const float* wts,
-                          void* act, float* y, float* out, void* stream) {
+                          int E, int top, float limit, int glu, const int* ids, const int* sorted, const int* tile_info, const float* wts,
+                          void* act, float* y, float* out, const float* add, void* stream) {
   OI_REQUIRE(rows >= 0 && W > 0 && F > 0 && E > 0 && top > 0, "moe_experts: bad sizes");
   if (rows == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
@@ -479,55 +511,55 @@ OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w
     const dim3 v1(pairs, (F + 15) / 16), v2(pairs, (W + 15) / 16);
     if (dtype == OI_F32) {
       oi_launch(moe_gemv_kernel<float, float, true>, v1, 128, (size_t)W * 4, s, (const float*)x, ldx, top, (const float*)w_gate_up,
-                (long long)2 * F * W, (float*)act, (long long)F, ids, F, W, limit);
+                (long long)2 * F * W, (float*)act, (long long)F, ids, F, W, limit, glu);
       OI_CHECK_LAUNCH();
       oi_launch(moe_gemv_kernel<float, float, false>, v2, 128, (size_t)F * 4, s, (const float*)act, (long long)F, 0, (const float*)w_down,
-                (long long)W * F, y, (long long)W, ids, W, F, 0.f);
+                (long long)W * F, y, (long long)W, ids, W, F, 0.f, 0);
     } else if (dtype == OI_BF16) {
       oi_launch(moe_gemv_kernel<bf16, bf16, true>, v1, 128, (size_t)W * 4, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up,
-                (long long)2 * F * W, (bf16*)act, (long long)F, ids, F, W, limit);
+                (long long)2 * F * W, (bf16*)act, (long long)F, ids, F, W, limit, glu);
       OI_CHECK_LAUNCH();
       oi_launch(moe_gemv_kernel<bf16, float, false>, v2, 128, (size_t)F * 4, s, (const bf16*)act, (long long)F, 0, (const bf16*)w_down,
-                (long long)W * F, y, (long long)W, ids, W, F, 0.f);
+                (long long)W * F, y, (long long)W, ids, W, F, 0.f, 0);
     } else {
       OI_REQUIRE(false, "moe_experts: unknown dtype code %d", dtype);
     }
     OI_CHECK_LAUNCH();
-    oi_launch(moe_combine_kernel, cblocks, 256, 0, s, out, (const float*)y, wts, top, W, n_out);
+    oi_launch(moe_combine_kernel, cblocks, 256, 0, s, out, (const float*)y, wts, top, W, n_out, add);
     OI_CHECK_LAUNCH();
     return OI_OK;
   }
   const dim3 g1(max_tiles, (F + kTileN - 1) / kTileN), g2(max_tiles, (W + kTileN - 1) / kTileN);
   if (dtype == OI_F32) {
     oi_launch(moe_gemm_kernel<float, float, true>, g1, 256, 0, s, (const float*)x, ldx, top, (const float*)w_gate_up, (long long)2 * F * W,
-              (float*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit);
+              (float*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit, glu);
     OI_CHECK_LAUNCH();
     oi_launch(moe_gemm_kernel<float, float, false>, g2, 256, 0, s, (const float*)act, (long long)F, 0, (const float*)w_down, (long long)W * F,
-              y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f);
+              y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f, 0);
   } else if (dtype == OI_BF16) {
     // tensor cores when every row of the operands starts on a 16-byte boundary
     const bool tc1 = W % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w_gate_up % 16 == 0;
     const bool tc2 = F % 8 == 0 && (uintptr_t)act % 16 == 0 && (uintptr_t)w_down % 16 == 0;
     if (tc1)
       oi_launch(moe_gemm_mma_kernel<bf16, true>, g1, 256, 0, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up, (long long)2 * F * W,
-                (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit);
+                (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit, glu);
     else
       oi_launch(moe_gemm_kernel<bf16, bf16, true>, g1, 256, 0, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up, (long long)2 * F * W,
-                (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit);
+                (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit, glu);
     OI_CHECK_LAUNCH();
     if (tc2)
       oi_launch(moe_gemm_mma_kernel<float, false>, g2, 256, 0, s, (const bf16*)act, (long long)F, 0, (const bf16*)w_down, (long long)W * F,
-                y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f);
+                y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f, 0);
     else
       oi_launch(moe_gemm_kernel<bf16, float, false>, g2, 256, 0, s, (const bf16*)act, (long long)F, 0, (const bf16*)w_down, (long long)W * F,
-                y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f);
+                y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f, 0);
   } else {
     OI_REQUIRE(false, "moe_experts: unknown dtype code %d", dtype);
   }
   OI_CHECK_LAUNCH();
   const size_t n = (size_t)rows * W;
   const int blocks = (int)((n + 255) / 256 > 148 * 16 ? 148 * 16 : (n + 255) / 256);
-  oi_launch(moe_combine_kernel, blocks, 256, 0, s, out, (const float*)y, wts, top, W, n);
+  oi_launch(moe_combine_kernel, blocks, 256, 0, s, out, (const float*)y, wts, top, W, n, add);
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

@@ -30,14 +30,23 @@ typedef struct OiStreamEpilogue {
   float* ssq_out;
 } OiStreamEpilogue;
 
+// What an attention layer may do to its scores beyond scale, mask and softmax; everything off when zero / null.
+typedef struct OiScoreMods {
+  const float* sinks;    // [nq] float32: one more term exp(sinks[h]) in the softmax's denominator, without a key or a value
+  const float* slopes;   // [nq] float32: slopes[h] * (i - j) is taken off the score of key j for the query at position i
+  float softcap;         // > 0: score <- softcap * tanh(score / softcap), before the slope
+  float qt_coef;         // qt_every > 0: the score of the query at position p is multiplied by
+  int qt_every;          //   1 + qt_coef * ln(floor((p + 1) / qt_every) + 1), before the cap
+} OiScoreMods;
+
 // argmax_noalloc.cu
 OI_API int oi_argmax_noalloc(int* out, const float* logits, int rows, int vocab, long long row_stride, void* stream);
 
 // attention_generic.cu
 OI_API int oi_attention_generic(const void* q, int q_row_stride, void* out, int out_row_stride, int dtype, const void*
        k_cache, const void* v_cache, long long page_stride, int page_size, const int* block_table, int bt_stride,
-       const int* token_req, const int* positions, int tokens, int nq, int nkv, int hd, float scale, int window, void*
-       stream);
+       const int* token_req, const int* positions, int tokens, int nq, int nkv, int hd, float scale, int window,
+       const OiScoreMods* mods, void* stream);
 
 // attention_mma.cu
 OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
@@ -112,8 +121,20 @@ OI_API int oi_moe_small(int pairs, int experts);
 OI_API int oi_moe_route(const void* x, int dtype, long long ldx, const void* w_router, int w_dtype, int rows, int K, int
        E, int top, int* ids, float* wts, int* sorted, int* tile_info, void* stream);
 OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w_gate_up, const void* w_down, int rows,
-       int W, int F, int E, int top, float limit, const int* ids, const int* sorted, const int* tile_info, const float*
-       wts, void* act, float* y, float* out, void* stream);
+       int W, int F, int E, int top, float limit, int glu, const int* ids, const int* sorted, const int* tile_info, const float*
+       wts, void* act, float* y, float* out, const float* add, void* stream);
+
+OI_API int oi_moe_route_table(const int* token_ids, const int* table, int rows, int vocab, int E, int top, int* ids, float*
+       wts, int* sorted, int* tile_info, void* stream);
+
+// parallel_ops.cu: a latent with a rotated key part, the joint residual add, a gate times a per-token embedding
+OI_API int oi_latent_rope_store(void* pages, long long page_stride, int page_size, int row_elems, void* proj, long long
+       proj_stride, int dtype, int tokens, int latent_off, int rank, const void* w, int w_dtype, float eps, float
+       w_offset, int rot_half, const float* cos_tab, const float* sin_tab, int max_pos, const int* positions, const int*
+       slots, int heads, int q_head_stride, int q_rot_off, int store, void* stream);
+OI_API int oi_add2_cast(float* x, const float* a, const float* b, void* low, int low_dtype, long long n, void* stream);
+OI_API int oi_token_gate(void* g, long long g_stride, int dtype, const int* token_ids, const void* table, int table_dtype,
+       long long table_stride, int vocab, int off, int dim, int tokens, void* stream);
 
 // gemm_stream.cu / gemm_tcgen05.cu: the gate/up product with a gated activation that takes a limit
 OI_API int oi_gemm_stream_glu(void* out, int out_dtype, long long ldc, const void* x, long long ldx, const void* W, long
@@ -282,6 +303,7 @@ typedef struct OiAttnLayer {
   int write_kv;              // the call owns its cache: keys and values of the step's rows are stored
   int rope_mode;             // 0: q is ready and the cache is written; 1: norm + rotation + cache write first (in its own
                              // kernel, or inside the decode kernel when the step says fuse_rope)
+  OiScoreMods mods;          // sink, distance slopes, cap and query temperature (all off for a plain softmax)
 } OiAttnLayer;
 
 OI_API int oi_attention_layer(const OiAttnStep* step, const OiAttnLayer* layer, void* stream);

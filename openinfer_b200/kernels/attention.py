@@ -52,9 +52,11 @@ def run_attention(step: "native.AttnStep", layer: "native.AttnLayer") -> None:
 def attention_layer(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, nq: int, nkv: int,
                     hd: int, scale: float, window: Optional[int], *, q_norm_w=None, k_norm_w=None, eps: float = 0.0,
                     weight_offset: float = 0.0, cos=None, sin=None, write_kv: bool = True, rope_mode: int = 1,
-                    interleaved: bool = False) -> "native.AttnLayer":
-    """The description of one layer's attention call (csrc/oi_api.h, OiAttnLayer)."""
+                    interleaved: bool = False, mods: Optional["native.ScoreMods"] = None) -> "native.AttnLayer":
+    """The description of one layer's attention call (csrc/oi_api.h, OiAttnLayer). ``mods``: what the layer does to its
+    scores beyond scale, mask and softmax (sink, distance slopes, cap, query temperature)."""
     _check_layer_operands(qkv, out, k_cache, v_cache, q_norm_w, k_norm_w, cos, sin, hd)
+    extra = {} if mods is None else {"mods": mods}
     norm_dtype = 0
     if q_norm_w is not None:
         norm_dtype = 1 if q_norm_w.dtype == torch.bfloat16 else 0
@@ -66,7 +68,7 @@ def attention_layer(qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         nq=nq, nkv=nkv, hd=hd, window=int(window) if window else 0, scale=float(scale), eps=float(eps),
         w_offset=float(weight_offset), norm_dtype=norm_dtype, rot_half=0 if cos is None else cos.shape[1],
         max_pos=0 if cos is None else cos.shape[0], interleaved=1 if interleaved else 0, write_kv=1 if write_kv else 0,
-        rope_mode=rope_mode)
+        rope_mode=rope_mode, **extra)
 
 
 def _check_layer_operands(qkv, out, k_cache, v_cache, q_norm_w, k_norm_w, cos, sin, hd) -> None:
@@ -338,6 +340,7 @@ def tcgen05_status() -> int:
 
 
 FUSE_ROPE_IN_DECODE = True
+MODS_ON_TENSOR_CORES = False   # layers that modify their scores run on the general kernel
 
 
 def decode_takes_rope(qkv: torch.Tensor, ctx, group_step, nq: int, nkv: int, hd: int, window, cos, q_norm_w,
@@ -365,10 +368,11 @@ def decode_takes_rope(qkv: torch.Tensor, ctx, group_step, nq: int, nkv: int, hd:
 
 
 def attention_step(ctx, group_step, qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, page_stride: int,
-                   nq: int, nkv: int, hd: int, window, cos=None, q_norm_w=None) -> "native.AttnStep":
+                   nq: int, nkv: int, hd: int, window, cos=None, q_norm_w=None, mods: bool = False) -> "native.AttnStep":
     """What every attention call of one geometry shares in this step (csrc/oi_api.h, OiAttnStep): the step's metadata
-    on the device, which kernels take it, and their work items. Made once per step and geometry."""
-    key = ("attention_step", id(group_step), nq, nkv, hd, window, qkv.dtype, qkv.stride(0), out.stride(0), cos is not None)
+    on the device, which kernels take it, and their work items. Made once per step and geometry. ``mods``: the layers of
+    this geometry modify their scores (OiScoreMods), which not every kernel takes."""
+    key = ("attention_step", id(group_step), nq, nkv, hd, window, qkv.dtype, qkv.stride(0), out.stride(0), cos is not None, mods)
     step = ctx.scratch.get(key)
     if step is not None:
         return step
@@ -376,7 +380,7 @@ def attention_step(ctx, group_step, qkv: torch.Tensor, out: torch.Tensor, k_cach
     bt = group_step.block_table
     # the tensor-core kernels: bfloat16, head_dim 32, 64 or 128
     tensor_core = (qkv.dtype == torch.bfloat16 and hd in (32, 64, 128) and group <= ROWS_PER_CTA_LARGE
-                   and qkv.stride(0) % 2 == 0 and page_stride % 8 == 0)
+                   and qkv.stride(0) % 2 == 0 and page_stride % 8 == 0 and not (mods and not MODS_ON_TENSOR_CORES))
     def ptr(obj, name):     # a step that only runs kernels which do not read a tensor may leave it out
         t = getattr(obj, name, None)
         return 0 if t is None else t.data_ptr()

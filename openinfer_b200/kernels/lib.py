@@ -30,7 +30,7 @@ _SIGNATURES = {
     "oi_scale_cap": [P, I, L, F, F, P],
     "oi_silu_mul": [P, P, I, I, I, I, I, P],
     "oi_qk_norm_rope_kv": [P, I, I, I, I, I, I, P, P, I, F, F, P, P, I, I, P, P, P, P, L, I, I, I, P],
-    "oi_attention_generic": [P, I, P, I, I, P, P, L, I, P, I, P, P, I, I, I, I, F, I, P],
+    "oi_attention_generic": [P, I, P, I, I, P, P, L, I, P, I, P, P, I, I, I, I, F, I, P, P],
     "oi_gemm_generic": [P, I, P, I, P, I, I, I, I, L, L, L, P],
     "oi_argmax": [P, P, I, I, L, P, P, P],
     "oi_token_logprobs": [P, L, I, P, P, P, I, I, P, P, P, P],
@@ -68,8 +68,12 @@ _SIGNATURES = {
     "oi_scaled_sum": [P, P, P, F, F, L, P],
     "oi_moe_max_tiles": [I, I],
     "oi_moe_route": [P, I, L, P, I, I, I, I, I, P, P, P, P, P],
-    "oi_moe_experts": [P, I, L, P, P, I, I, I, I, I, F, P, P, P, P, P, P, P, P],
+    "oi_moe_experts": [P, I, L, P, P, I, I, I, I, I, F, I, P, P, P, P, P, P, P, P, P],
+    "oi_moe_route_table": [P, P, I, I, I, I, P, P, P, P, P],
     "oi_moe_small": [I, I],
+    "oi_latent_rope_store": [P, L, I, I, P, L, I, I, I, I, P, I, F, F, I, P, P, I, P, P, I, I, I, I, P],
+    "oi_add2_cast": [P, P, P, P, I, L, P],
+    "oi_token_gate": [P, L, I, P, P, I, L, I, I, I, I, P],
     "oi_gemm_stream_glu": [P, I, L, P, L, P, L, I, I, I, I, I, F, P],
     "oi_gemm_tcgen05_glu": [P, L, P, L, P, L, I, I, I, I, I, F, P],
 }

@@ -45,6 +45,10 @@ class AttnStep(Structure):
     ]
 
 
+class ScoreMods(Structure):
+    _fields_ = [("sinks", c_void_p), ("slopes", c_void_p), ("softcap", c_float), ("qt_coef", c_float), ("qt_every", c_int)]
+
+
 class AttnLayer(Structure):
     _fields_ = [
         ("qkv", c_void_p), ("out", c_void_p), ("k_cache", c_void_p), ("v_cache", c_void_p),
@@ -54,6 +58,7 @@ class AttnLayer(Structure):
         ("scale", c_float), ("eps", c_float), ("w_offset", c_float),
         ("norm_dtype", c_int), ("rot_half", c_int), ("max_pos", c_int),
         ("interleaved", c_int), ("write_kv", c_int), ("rope_mode", c_int),
+        ("mods", ScoreMods),
     ]
 
 

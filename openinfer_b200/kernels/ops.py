@@ -240,9 +240,11 @@ def qk_norm_rope_kv(qkv: torch.Tensor, nq: int, nkv: int, hd: int, *, q_norm_w: 
 def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                       page_stride: int, page_size: int, block_table: torch.Tensor, token_req: torch.Tensor,
                       positions: torch.Tensor, nq: int, nkv: int, hd: int, scale: float,
-                      window: Optional[int] = None) -> torch.Tensor:
+                      window: Optional[int] = None, mods=None) -> torch.Tensor:
     """Paged causal attention, one warp per (token, head). ``q`` is [tokens, >= nq*hd] with
-    any row stride; ``out`` is [tokens, nq*hd]; ``block_table`` is int32 [requests, max_pages]."""
+    any row stride; ``out`` is [tokens, nq*hd]; ``block_table`` is int32 [requests, max_pages]; ``mods`` a
+    ``native.ScoreMods`` (sink, slopes, cap, query temperature) or None."""
+    import ctypes
     _cuda(q, out, k_cache, v_cache, block_table, token_req, positions)
     _i32(block_table, "block_table")
     _i32(token_req, "token_req")
@@ -257,7 +259,8 @@ def attention_generic(q: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor,
         q.data_ptr(), q.stride(0), out.data_ptr(), out.stride(0), _code(q, "attention"), k_cache.data_ptr(),
         v_cache.data_ptr(), int(page_stride), int(page_size), block_table.data_ptr(), block_table.stride(0),
         token_req.data_ptr(), positions.data_ptr(), tokens, nq, nkv, hd, float(scale),
-        int(window) if window else 0, _stream()), "attention")
+        int(window) if window else 0, ctypes.cast(ctypes.pointer(mods), ctypes.c_void_p) if mods is not None else None,
+        _stream()), "attention")
     return out
 
 
@@ -642,8 +645,27 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int):
     return ids, wts, order, tiles
 
 
-def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, routing, limit: float) -> torch.Tensor:
-    """sum_j weight_j * down_e(act(gate_e x, up_e x)) over a row's chosen experts; float32 [rows, width].
+def moe_route_table(token_ids: torch.Tensor, table: torch.Tensor, experts: int):
+    """Routing by the token id: row t uses the experts ``table[token_ids[t], :]`` (int32 [vocab, top]), each weighted 1 / top.
+    Returns what ``moe_route`` returns."""
+    _cuda(token_ids, table)
+    _i32(token_ids, "moe_route_table token ids")
+    _i32(table, "moe_route_table table")
+    rows, (vocab, top) = token_ids.numel(), table.shape
+    L = _lib.load()
+    ids = torch.empty((rows, top), dtype=torch.int32, device=table.device)
+    wts = torch.empty((rows, top), dtype=torch.float32, device=table.device)
+    order = torch.empty(rows * top, dtype=torch.int32, device=table.device)
+    tiles = torch.empty(3 * L.oi_moe_max_tiles(rows * top, experts) + 1, dtype=torch.int32, device=table.device)
+    _lib.check(L.oi_moe_route_table(token_ids.data_ptr(), table.data_ptr(), rows, vocab, int(experts), top, ids.data_ptr(), wts.data_ptr(),
+                                    order.data_ptr(), tiles.data_ptr(), _stream()), "moe_route_table")
+    return ids, wts, order, tiles
+
+
+def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, routing, limit: float,
+                act: str = "swiglu_clamp", add: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """sum_j weight_j * down_e(act(gate_e x, up_e x)) over a row's chosen experts (+ ``add``, float32 [rows, width], when
+    given: an expert every row uses); float32 [rows, width].
     ``w_gate_up`` [E, 2 F, W] (F gate rows, then F up rows), ``w_down`` [E, W, F], in x's type."""
     ids, wts, order, tiles = routing
     _cuda(x, w_gate_up, w_down)
@@ -653,10 +675,67 @@ def moe_experts(x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, 
     if w_gate_up.dtype != x.dtype or w_down.dtype != x.dtype or w_down.shape != (E, W, F2 // 2) or x.stride(1) != 1 \
             or not (w_gate_up.is_contiguous() and w_down.is_contiguous()):
         raise KernelError("moe_experts: the experts' weights must be contiguous, in x's type, [E, 2F, W] and [E, W, F]")
-    act = torch.empty((rows * top, F2 // 2), dtype=x.dtype, device=x.device)
+    if add is not None and (add.dtype != torch.float32 or add.shape != (rows, W) or not add.is_contiguous()):
+        raise KernelError("moe_experts: add must be a contiguous float32 [rows, width] tensor")
+    _cuda(add)
+    hidden = torch.empty((rows * top, F2 // 2), dtype=x.dtype, device=x.device)
     y = torch.empty((rows * top, W), dtype=torch.float32, device=x.device)
     out = torch.empty((rows, W), dtype=torch.float32, device=x.device)
     _lib.check(_lib.load().oi_moe_experts(x.data_ptr(), _code(x, "moe_experts"), x.stride(0), w_gate_up.data_ptr(), w_down.data_ptr(), rows,
-                                          W, F2 // 2, E, top, float(limit), ids.data_ptr(), order.data_ptr(), tiles.data_ptr(), wts.data_ptr(),
-                                          act.data_ptr(), y.data_ptr(), out.data_ptr(), _stream()), "moe_experts")
+                                          W, F2 // 2, E, top, float(limit), glu_code(act), ids.data_ptr(), order.data_ptr(), tiles.data_ptr(),
+                                          wts.data_ptr(), hidden.data_ptr(), y.data_ptr(), out.data_ptr(), _ptr(add), _stream()), "moe_experts")
     return out
+
+
+# ---------------------------------------------------------------------------
+# blocks whose sublayers share one norm; a latent with a rotated key part (csrc/parallel_ops.cu)
+# ---------------------------------------------------------------------------
+def latent_rope_store(pages: Optional[torch.Tensor], page_stride: int, proj: torch.Tensor, latent_off: int, rank: int,
+                      weight: Optional[torch.Tensor], eps: float, weight_offset: float, cos: torch.Tensor, sin: torch.Tensor,
+                      positions: torch.Tensor, slots: Optional[torch.Tensor], heads: int, q_head_stride: int, q_rot_off: int,
+                      store: bool = True) -> None:
+    """One pass over the fused input product ``proj`` [tokens, queries | latent, rotated key part | ...]: every head's rotated
+    query part (``2 * cos.shape[1]`` numbers at ``h * q_head_stride + q_rot_off``) is turned in place by its row's position;
+    with ``store`` the latent (``rank`` numbers at ``latent_off``) is RMS-normed with ``weight`` and written, followed by the
+    turned key part that lies behind it, to the row's slot of ``pages`` [pages, page_size, 1, row_elems] (the rest zero)."""
+    _cuda(pages, proj, weight, cos, sin, positions, slots)
+    _i32(positions, "latent_rope_store positions")
+    _i32(slots, "latent_rope_store slots")
+    if cos.dtype != torch.float32 or sin.shape != cos.shape or not (cos.is_contiguous() and sin.is_contiguous()) or proj.stride(1) != 1:
+        raise KernelError("latent_rope_store: cos/sin must be contiguous float32 tables of one shape, proj contiguous along a row")
+    max_pos, rot_half = cos.shape
+    if store and (pages is None or pages.dtype != proj.dtype or weight is None or weight.numel() != rank or slots is None):
+        raise KernelError("latent_rope_store: the store needs pages of proj's type, the norm's weight and the rows' slots")
+    tokens = proj.shape[0]
+    _lib.check(_lib.load().oi_latent_rope_store(
+        _ptr(pages), int(page_stride), pages.shape[1] if pages is not None else 1, pages.shape[-1] if pages is not None else rank + 2 * rot_half,
+        proj.data_ptr(), proj.stride(0), _code(proj, "latent_rope_store"), tokens, int(latent_off), int(rank), _ptr(weight),
+        _code(weight, "latent_rope_store weight") if weight is not None else 0, float(eps), float(weight_offset), rot_half,
+        cos.data_ptr(), sin.data_ptr(), max_pos, positions.data_ptr(), _ptr(slots), int(heads), int(q_head_stride), int(q_rot_off),
+        1 if store else 0, _stream()), "latent_rope_store")
+
+
+def add2_cast(x: torch.Tensor, a: torch.Tensor, b: Optional[torch.Tensor] = None, low: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x <- x + a (+ b) on contiguous float32 tensors of one shape; ``low`` (same shape, float32 or bfloat16) gets the new x rounded."""
+    _cuda(x, a, b, low)
+    for t in (x, a, b):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.shape != x.shape):
+            raise KernelError("add2_cast: x, a and b must be contiguous float32 tensors of one shape")
+    if low is not None and (low.shape != x.shape or not low.is_contiguous()):
+        raise KernelError("add2_cast: low must be contiguous and shaped like x")
+    _lib.check(_lib.load().oi_add2_cast(x.data_ptr(), a.data_ptr(), _ptr(b), _ptr(low), _code(low, "add2_cast low") if low is not None else 0,
+                                        x.numel(), _stream()), "add2_cast")
+    return x
+
+
+def token_gate(g: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, off: int) -> torch.Tensor:
+    """g [tokens, dim] <- gelu_tanh(g) * table[token_ids[t], off : off + dim] in place (table [vocab, >= off + dim])."""
+    _cuda(g, token_ids, table)
+    _i32(token_ids, "token_gate token ids")
+    tokens, dim = g.shape
+    if g.stride(1) != 1 or table.dim() != 2 or table.stride(1) != 1 or table.shape[1] < off + dim or token_ids.numel() != tokens:
+        raise KernelError(f"token_gate: g={tuple(g.shape)} table={tuple(table.shape)} off={off}")
+    _lib.check(_lib.load().oi_token_gate(g.data_ptr(), g.stride(0), _code(g, "token_gate"), token_ids.data_ptr(), table.data_ptr(),
+                                         _code(table, "token_gate table"), table.stride(0), table.shape[0], int(off), dim, tokens,
+                                         _stream()), "token_gate")
+    return g

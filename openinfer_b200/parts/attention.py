@@ -12,6 +12,13 @@ kernels: the cached row is ``head_dim`` (a multiple of 8 that holds both), the p
 they are loaded (zeros change neither a score nor a value), and a per-head norm over qk_dim numbers is the norm over
 head_dim with eps * qk_dim / head_dim whose result is long by sqrt(head_dim / qk_dim) in q and in k alike, which the
 softmax scale takes back.
+
+Optional, all from the spec: a short causal filter over time on every channel of q, k and v directly behind the
+projections (its last taps - 1 input rows are per-request state); a query temperature that grows with the logarithm of the
+position; a cap on the scores (cap * tanh(s / cap)); a distance bias slope_h * (i - j) with slope_h = 2^(-e (h + 1) / H);
+a learned sink per head in the softmax's denominator; a sigmoid gate per head on the attention's output, read off the
+mixer's input by rows appended to the fused projection. Temperature, cap, bias and sink are applied to the float32 scores
+inside the attention kernels (csrc/oi_api.h, OiScoreMods).
 """
 from __future__ import annotations
 
@@ -19,8 +26,9 @@ from typing import Dict, Optional
 
 import torch
 
-from ..cache.manager import KvNeed
+from ..cache.manager import KvNeed, StateNeed
 from ..kernels import attention as attn_kernels
+from ..kernels import native, ops
 from ..kernels.linear import linear
 from .base import CacheBinding, Mixer
 from .registry import build_position_encoding, register_mixer
@@ -48,6 +56,18 @@ class Attention(Mixer):
         self.norm_eps_factor = self.qk / s.head_dim
         self.scale = s.softmax_scale * (self.qk / s.head_dim if (s.qk_norm is not None and self.qk != s.head_dim) else 1.0)
         self.position = build_position_encoding(s.position)
+        if s.conv_taps < 0 or s.score_cap < 0.0 or s.distance_slope_exponent < 0.0:
+            raise ValueError("attention: conv_taps, score_cap and distance_slope_exponent cannot be negative")
+        if s.q_temperature is not None and int(s.q_temperature[1]) <= 0:
+            raise ValueError(f"attention: the query temperature's period must be positive, got {s.q_temperature[1]}")
+        self.qkv_cols = self.q_dim + 2 * self.kv_dim
+        self.gate_off = self.qkv_cols                      # the gate's columns of the fused projection, behind q | k | v
+        self.in_cols = -(-(self.qkv_cols + (s.num_heads if s.head_gate else 0)) // 8) * 8
+        self.has_mods = bool(s.sink or s.score_cap > 0.0 or s.distance_slope_exponent > 0.0 or s.q_temperature is not None)
+        self.w_conv: Optional[torch.Tensor] = None
+        self.sinks: Optional[torch.Tensor] = None
+        self.slopes: Optional[torch.Tensor] = None
+        self.mods = None
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
         self.q_norm_w: Optional[torch.Tensor] = None
@@ -57,6 +77,11 @@ class Attention(Mixer):
     def kv_need(self) -> Optional[KvNeed]:
         s = self.spec
         return KvNeed(s.num_kv_heads, s.head_dim, s.window)
+
+    def state_needs(self):
+        s = self.spec
+        # two copies that take turns: the filter's kernel reads a request's old rows while it leaves the new ones
+        return [StateNeed((s.conv_taps - 1, self.qkv_cols), "float32", phases=2)] if s.conv_taps > 1 else []
 
     def parameters(self) -> Dict[str, ParamInfo]:
         s = self.spec
@@ -69,6 +94,13 @@ class Attention(Mixer):
         if s.qk_norm is not None:
             p[s.q_norm_name] = ParamInfo((self.qk,), ("one_plus_normal", 0.02))
             p[s.k_norm_name] = ParamInfo((self.qk,), ("one_plus_normal", 0.02))
+        if s.conv_taps > 0:
+            for name, rows in ((s.q_name, s.num_heads * self.qk), (s.k_name, s.num_kv_heads * self.qk), (s.v_name, s.num_kv_heads * self.vd)):
+                p[name + s.conv_suffix] = ParamInfo((rows, s.conv_taps), ("normal_around", 0.2, 1.0 / s.conv_taps))
+        if s.sink:
+            p[s.sink_name] = ParamInfo((s.num_heads,), ("normal", 1.0))
+        if s.head_gate:
+            p[s.gate_name] = ParamInfo((s.num_heads, s.hidden_size), ("normal", s.hidden_size ** -0.5))
         return p
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -85,8 +117,20 @@ class Attention(Mixer):
             out[:, :size] = w.view(heads, size, -1)
             return out.view(heads * hd, -1)
 
-        self.w_qkv = torch.cat([rows_padded(q, s.num_heads, self.qk), rows_padded(k, s.num_kv_heads, self.qk),
-                                rows_padded(v, s.num_kv_heads, self.vd)], dim=0).contiguous()
+        fused = [rows_padded(q, s.num_heads, self.qk), rows_padded(k, s.num_kv_heads, self.qk), rows_padded(v, s.num_kv_heads, self.vd)]
+        if s.head_gate:
+            g = tensors[s.gate_name]
+            if g.dtype != q.dtype:
+                raise ValueError("the gate's projection must be stored in the dtype of q, k and v to be fused")
+            fused.append(g)
+            if self.in_cols > self.qkv_cols + s.num_heads:
+                fused.append(torch.zeros((self.in_cols - self.qkv_cols - s.num_heads, q.shape[1]), dtype=q.dtype, device=q.device))
+        self.w_qkv = torch.cat(fused, dim=0).contiguous()
+        if s.conv_taps > 0:
+            names = ((s.q_name, s.num_heads, self.qk), (s.k_name, s.num_kv_heads, self.qk), (s.v_name, s.num_kv_heads, self.vd))
+            self.w_conv = torch.cat([rows_padded(tensors[n + s.conv_suffix], heads, size) for n, heads, size in names], dim=0).contiguous()
+        if s.sink:
+            self.sinks = tensors[s.sink_name].to(torch.float32).contiguous()
         o = tensors[s.o_name]
         if self.vd != hd:
             wide = torch.zeros((o.shape[0], s.num_heads, hd), dtype=o.dtype, device=o.device)
@@ -108,6 +152,15 @@ class Attention(Mixer):
 
     def prepare(self, device: torch.device, dtype: torch.dtype) -> None:
         self.tables = self.position.rotation_tables(device)
+        s = self.spec
+        if s.distance_slope_exponent > 0.0:
+            h = torch.arange(1, s.num_heads + 1, dtype=torch.float64)
+            self.slopes = torch.pow(2.0, -s.distance_slope_exponent * h / s.num_heads).to(torch.float32).to(device)
+        if self.has_mods:
+            coef, every = s.q_temperature if s.q_temperature is not None else (0.0, 0)
+            self.mods = native.ScoreMods(sinks=None if self.sinks is None else self.sinks.data_ptr(),
+                                         slopes=None if self.slopes is None else self.slopes.data_ptr(),
+                                         softcap=float(s.score_cap), qt_coef=float(coef), qt_every=int(every))
 
     takes_out_dtype = True
 
@@ -117,19 +170,32 @@ class Attention(Mixer):
             raise RuntimeError("attention needs a cache binding")
         group = ctx.groups[binding.kv.group]
         k_cache, v_cache, page_stride = ctx.cache.kv_views(binding.kv)
-        w = self.w_qkv if binding.owns_kv else self.w_qkv[: self.q_dim]
-        qkv = linear(x, w)
+        if binding.owns_kv:
+            w = self.w_qkv
+        elif s.head_gate or s.conv_taps > 0:
+            raise RuntimeError("attention: a layer with a gate or a filter owns its cache")
+        else:
+            w = self.w_qkv[: self.q_dim]
+        qkv = raw = linear(x, w)
+        if s.conv_taps > 0:
+            # the filter over time on the q | k | v columns; the request's last taps - 1 rows are carried in its state slot
+            qkv = torch.empty((x.shape[0], self.qkv_cols), dtype=x.dtype, device=x.device)
+            state = ctx.cache.state_tensor(binding.states[0]) if s.conv_taps > 1 else None
+            ops.short_conv_act(qkv, raw[:, : self.qkv_cols], self.w_conv, state, ctx.cu_seqlens, ctx.token_req, ctx.state_slots,
+                               ctx.state_phase, act="none", add_input=False)
         cos, sin = self.tables if self.tables is not None else (None, None)
         qn = s.qk_norm
         out = torch.empty((x.shape[0], self.q_dim), dtype=x.dtype, device=x.device)
         # One native call: the norm + rotation + cache write (in a kernel of its own, or inside the decode kernel when
         # the step is single tokens in one wave), then the attention kernel(s) that take the step's shape.
         step = attn_kernels.attention_step(ctx, group, qkv, out, k_cache, page_stride, s.num_heads, s.num_kv_heads,
-                                           s.head_dim, s.window, cos=cos, q_norm_w=self.q_norm_w)
+                                           s.head_dim, s.window, cos=cos, q_norm_w=self.q_norm_w, mods=self.has_mods)
         layer = attn_kernels.attention_layer(
             qkv, out, k_cache, v_cache, s.num_heads, s.num_kv_heads, s.head_dim, self.scale, s.window,
             q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, eps=qn.eps * self.norm_eps_factor if qn else 0.0,
             weight_offset=qn.weight_offset if qn else 0.0, cos=cos, sin=sin, write_kv=binding.owns_kv, rope_mode=1,
-            interleaved=bool(getattr(s.position, "interleaved", False)))
+            interleaved=bool(getattr(s.position, "interleaved", False)), mods=self.mods)
         attn_kernels.run_attention(step, layer)
+        if s.head_gate:
+            ops.head_gate(out, raw[:, self.gate_off: self.gate_off + s.num_heads], s.num_heads, s.head_dim)
         return linear(out, self.w_o, out_dtype=out_dtype)

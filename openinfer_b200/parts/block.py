@@ -134,6 +134,60 @@ class BranchNormBlock(Block):
         return h, None
 
 
+@register_block("shared_norm")
+class SharedNormBlock(Block):
+    """x <- x + (mixer(h) + ff(h)) with h = norm(x): ONE norm whose output both sublayers read, and one add of their sum.
+    The feed-forward is optional. With ``token_input`` the block ends with a per-token input (``stream.TokenInput``).
+
+    The stream is float32 whatever the model's type. The norm reads it and writes h in the model's type; the sublayers
+    return float32; one kernel adds both to the stream and leaves the new stream rounded to the model's type for the
+    product that reads it next (the token input's gate)."""
+
+    stream_dtype = torch.float32
+
+    def __init__(self, spec: BlockSpec) -> None:
+        super().__init__(spec)
+        self._mixer = build_mixer(spec.mixer)
+        self.feed_forward = build_feed_forward(spec.feed_forward) if spec.feed_forward is not None else None
+        self.norm = build_norm(spec.input_norm)
+        self.token_input = build_stream_part(spec.token_input) if spec.token_input is not None else None
+        if not isinstance(self.norm, RmsNorm):
+            raise ValueError("a shared_norm block needs an rms norm")
+        for part in (self._mixer, self.feed_forward):
+            if part is not None and not getattr(part, "takes_out_dtype", False):
+                raise ValueError(f"a shared_norm block needs parts that can return float32, {type(part).__name__} cannot")
+
+    @property
+    def mixer(self):
+        return self._mixer
+
+    def sub_parts(self) -> Dict[str, Part]:
+        s = self.spec
+        parts: Dict[str, Part] = {s.input_norm_name: self.norm, s.mixer_name: self._mixer}
+        if self.feed_forward is not None:
+            parts[s.feed_forward_name] = self.feed_forward
+        if self.token_input is not None:
+            parts[s.token_input_name] = self.token_input
+        return parts
+
+    def forward(self, h: torch.Tensor, pending: Optional[torch.Tensor], ctx,
+                binding: CacheBinding) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        if h.dtype != torch.float32 or h.dim() != 2 or pending is not None:
+            raise RuntimeError("a shared_norm block takes one float32 stream with no branch pending")
+        dtype = ctx.scratch["model_dtype"]
+        ctx.scratch.pop("stream_low", None)
+        x = self.norm(h, out_dtype=dtype)
+        a = self._mixer.forward(x, ctx, binding, out_dtype=torch.float32)
+        m = self.feed_forward.forward(x, ctx, out_dtype=torch.float32) if self.feed_forward is not None else None
+        low = None
+        if self.token_input is not None and dtype != torch.float32:
+            low = torch.empty(h.shape, dtype=dtype, device=h.device)
+        ops.add2_cast(h, a, m, low)
+        if self.token_input is not None:
+            self.token_input.forward(h, low if low is not None else h, ctx)
+        return h, None
+
+
 @dataclasses.dataclass
 class PendingBranch:
     """A sublayer's result that has not reached the streams yet, with the coefficients it comes back by (None: added as

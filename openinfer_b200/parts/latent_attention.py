@@ -10,6 +10,14 @@ float64 and rounded once to the weights' type: queries and outputs then come str
 every step ("runtime": one small product per head before and after the attention). Cached rows are padded with zeros to
 a multiple of eight elements, which changes neither scores nor outputs.
 
+With ``rope_dim`` > 0 every head's query has a rotated part behind its ``qk_dim`` unrotated numbers and the down-projection
+one shared rotated key part behind the latent (not normed); their dot product is added to the score. The cached row is
+then [latent, rotated key part] and the absorbed query [Wuk_h^T q_h, rotated query part]: still one multi-query attention
+over one cached tensor, whose result's first ``latent_rank`` numbers are sum_s p_s c_s (the rest is not read). One kernel
+norms the latent, turns the key part, stores both, and turns the heads' query parts in place. A sink (a learned number per
+head in the softmax's denominator) is applied by the attention kernels; a gate per OUTPUT NUMBER (``gate_per`` "element")
+sits between the value up-projection and the output projection, so the former then runs in every step.
+
 A layer without a latent of its own (``has_latent`` False) reads the pages another layer wrote, with its own queries,
 up-projections, window and gate.
 """
@@ -21,10 +29,10 @@ import torch
 
 from ..cache.manager import KvNeed
 from ..kernels import attention as attn_kernels
-from ..kernels import ops
+from ..kernels import native, ops
 from ..kernels.linear import linear
 from .base import CacheBinding, Mixer
-from .registry import register_mixer
+from .registry import build_position_encoding, register_mixer
 from .spec import LatentAttentionSpec, ParamInfo
 
 
@@ -47,13 +55,29 @@ class LatentAttention(Mixer):
             raise ValueError(f"latent_attention: absorb must be 'weights' or 'runtime', got {s.absorb!r}")
         if s.window is not None and s.window <= 0:
             raise ValueError(f"latent_attention: window must be positive, got {s.window}")
-        self.row = _round_up(s.latent_rank, 8)          # elements of a cached row
+        if s.gate_per not in ("head", "element"):
+            raise ValueError(f"latent_attention: gate_per must be 'head' or 'element', got {s.gate_per!r}")
+        if s.rope_dim < 0 or s.rope_dim % 2:
+            raise ValueError(f"latent_attention: rope_dim must be even and not negative, got {s.rope_dim}")
+        if s.rope_dim:
+            if s.position is None or s.position.kind == "none" or s.position.rotary_dim != s.rope_dim:
+                raise ValueError("latent_attention: a rotated part needs a position encoding over exactly its numbers")
+            if s.absorb != "weights":
+                raise ValueError("latent_attention: a rotated part needs the key up-projection absorbed into the weights")
+        self.position = build_position_encoding(s.position) if s.rope_dim else None
+        self.tables = None
+        # the values' up-projection is multiplied into the output projection unless a gate sits between the two
+        self.absorb_values = s.absorb == "weights" and not (s.output_gate and s.gate_per == "element")
+        self.gate_cols = (s.num_heads * s.v_dim if s.gate_per == "element" else s.num_heads) if s.output_gate else 0
+        self.row = _round_up(s.latent_rank + s.rope_dim, 8)          # elements of a cached row
         if self.row > 512:
             raise ValueError(f"latent_attention: latent_rank {s.latent_rank} is beyond what the attention kernels take (512)")
         self.q_cols = s.num_heads * (self.row if s.absorb == "weights" else s.qk_dim)
         self.latent_off = self.q_cols
-        self.gate_off = self.latent_off + (s.latent_rank if s.has_latent else 0)
-        self.in_cols = _round_up(self.gate_off + (s.num_heads if s.output_gate else 0), 8)
+        self.gate_off = self.latent_off + (s.latent_rank + s.rope_dim if s.has_latent else 0)
+        self.in_cols = _round_up(self.gate_off + self.gate_cols, 8)
+        self.sinks: Optional[torch.Tensor] = None
+        self.mods = None
         self.w_in: Optional[torch.Tensor] = None         # [in_cols, hidden]: queries | latent | gate | zero rows
         self.w_out: Optional[torch.Tensor] = None        # [hidden, heads * row] ("weights") or [hidden, heads * v_dim]
         self.w_latent_norm: Optional[torch.Tensor] = None
@@ -67,17 +91,19 @@ class LatentAttention(Mixer):
         s = self.spec
         H, W, R = s.num_heads, s.hidden_size, s.latent_rank
         p = {
-            s.q_name: ParamInfo((H * s.qk_dim, W), ("normal", W ** -0.5)),
+            s.q_name: ParamInfo((H * (s.qk_dim + s.rope_dim), W), ("normal", W ** -0.5)),
             s.up_k_name: ParamInfo((H * s.qk_dim, R), ("normal", R ** -0.5)),
             s.up_v_name: ParamInfo((H * s.v_dim, R), ("normal", R ** -0.5)),
             s.out_name: ParamInfo((W, H * s.v_dim), ("normal", (H * s.v_dim) ** -0.5)),
         }
         if s.has_latent:
-            p[s.down_name] = ParamInfo((R, W), ("normal", W ** -0.5))
+            p[s.down_name] = ParamInfo((R + s.rope_dim, W), ("normal", W ** -0.5))
             if s.latent_norm is not None:
                 p[s.latent_norm_name] = ParamInfo((R,), ("one_plus_normal", 0.1))
         if s.output_gate:
-            p[s.gate_name] = ParamInfo((H, W), ("normal", W ** -0.5))
+            p[s.gate_name] = ParamInfo((self.gate_cols, W), ("normal", W ** -0.5))
+        if s.sink:
+            p[s.sink_name] = ParamInfo((H,), ("normal", 1.0))
         return p
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -88,13 +114,22 @@ class LatentAttention(Mixer):
         f64 = torch.float64
         uk = wuk.to(f64).view(H, D, R)
         uv = wuv.to(f64).view(H, V, R)
+        P = s.rope_dim
         if s.absorb == "weights":
+            wq_heads = wq.to(f64).view(H, D + P, W)
             q_rows = torch.zeros((H, row, W), dtype=f64, device=dev)
-            q_rows[:, :R] = torch.matmul(uk.transpose(1, 2), wq.to(f64).view(H, D, W))          # Wuk_h^T Wq_h
-            out_cols = torch.zeros((W, H, row), dtype=f64, device=dev)
-            out_cols[:, :, :R] = torch.einsum("whv,hvr->whr", wo.to(f64).view(W, H, V), uv)      # Wo_h Wuv_h
+            q_rows[:, :R] = torch.matmul(uk.transpose(1, 2), wq_heads[:, :D])                   # Wuk_h^T Wq_h
+            q_rows[:, R: R + P] = wq_heads[:, D:]                                               # the rotated part, as stored
             q_part = q_rows.view(H * row, W).to(dt)
-            self.w_out = out_cols.view(W, H * row).to(wo.dtype).contiguous()
+            if self.absorb_values:
+                out_cols = torch.zeros((W, H, row), dtype=f64, device=dev)
+                out_cols[:, :, :R] = torch.einsum("whv,hvr->whr", wo.to(f64).view(W, H, V), uv)  # Wo_h Wuv_h
+                self.w_out = out_cols.view(W, H * row).to(wo.dtype).contiguous()
+            else:
+                self.w_out = wo.contiguous()
+                up_v = torch.zeros((H, V, row), dtype=wuv.dtype, device=dev)
+                up_v[:, :, :R] = wuv.view(H, V, R)
+                self.w_up_v = up_v.contiguous()
         else:
             q_part = wq
             self.w_out = wo.contiguous()
@@ -112,12 +147,19 @@ class LatentAttention(Mixer):
                 raise ValueError("latent_attention: a latent without a norm has no kernel")
         if s.output_gate:
             parts.append(tensors[s.gate_name])
+        if s.sink:
+            self.sinks = tensors[s.sink_name].to(torch.float32).contiguous()
+            self.mods = native.ScoreMods(sinks=self.sinks.data_ptr())
         if any(p.dtype != dt for p in parts):
             raise ValueError("latent_attention: the input projections must be stored in one dtype to be fused")
         rows = sum(p.shape[0] for p in parts)
         if self.in_cols > rows:
             parts.append(torch.zeros((self.in_cols - rows, W), dtype=dt, device=dev))
         self.w_in = torch.cat(parts, dim=0).contiguous()
+
+    def prepare(self, device: torch.device, dtype: torch.dtype) -> None:
+        if self.position is not None:
+            self.tables = self.position.rotation_tables(device)
 
     def forward(self, x: torch.Tensor, ctx, binding: CacheBinding, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
         s = self.spec
@@ -129,7 +171,15 @@ class LatentAttention(Mixer):
         group = ctx.groups[binding.kv.group]
         pages, _, page_stride = ctx.cache.kv_views(binding.kv)
         proj = linear(x, self.w_in)                                        # [T, queries | latent | gate]
-        if s.has_latent:
+        if s.rope_dim:
+            # one pass: the latent's norm, the key part's rotation, both stored; the heads' query parts turned in place
+            ln = s.latent_norm
+            cos, sin = self.tables
+            ops.latent_rope_store(pages if s.has_latent else None, page_stride, proj, self.latent_off, s.latent_rank,
+                                  self.w_latent_norm if s.has_latent else None, ln.eps if ln else 0.0, ln.weight_offset if ln else 0.0,
+                                  cos, sin, ctx.positions, group.slot_mapping if s.has_latent else None, H, row, s.latent_rank,
+                                  store=s.has_latent)
+        elif s.has_latent:
             ln = s.latent_norm
             ops.latent_store(pages, page_stride, proj[:, self.latent_off: self.latent_off + s.latent_rank], self.w_latent_norm,
                              group.slot_mapping, s.latent_rank, ln.eps, ln.weight_offset)
@@ -140,15 +190,17 @@ class LatentAttention(Mixer):
             for h in range(H):
                 linear(proj[:, h * s.qk_dim: (h + 1) * s.qk_dim], self.w_up_k[h], out=q[:, h * row: (h + 1) * row])
         mixed = torch.empty((T, H * row), dtype=x.dtype, device=x.device)
-        step = attn_kernels.attention_step(ctx, group, q, mixed, pages, page_stride, H, 1, row, s.window)
+        step = attn_kernels.attention_step(ctx, group, q, mixed, pages, page_stride, H, 1, row, s.window, mods=self.mods is not None)
         layer = attn_kernels.attention_layer(q, mixed, pages, pages, H, 1, row, s.softmax_scale, s.window,
-                                             write_kv=False, rope_mode=0)
+                                             write_kv=False, rope_mode=0, mods=self.mods)
         attn_kernels.run_attention(step, layer)
-        if s.output_gate:
+        if s.output_gate and s.gate_per == "head":
             ops.head_gate(mixed, proj[:, self.gate_off: self.gate_off + H], H, row)
-        if s.absorb == "runtime":
+        if not self.absorb_values:
             heads_out = torch.empty((T, H * s.v_dim), dtype=x.dtype, device=x.device)
             for h in range(H):
                 linear(mixed[:, h * row: (h + 1) * row], self.w_up_v[h], out=heads_out[:, h * s.v_dim: (h + 1) * s.v_dim])
             mixed = heads_out
+            if s.output_gate and s.gate_per == "element":
+                ops.head_gate(mixed, proj[:, self.gate_off: self.gate_off + H * s.v_dim], H * s.v_dim, 1)
         return linear(mixed, self.w_out, out_dtype=out_dtype)

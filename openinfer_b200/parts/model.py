@@ -51,13 +51,19 @@ class Model:
         self._native_checked = False
 
     # ------------------------------------------------------------------ tensors
+    @staticmethod
+    def _tensor_name(prefix: str, local: str) -> str:
+        """A part's local tensor name under its prefix; a local name that opens with "/" is absolute (a tensor that
+        several parts share, such as a table all layers read)."""
+        return local[1:] if local.startswith("/") else prefix + local
+
     def expected_tensors(self) -> Dict[str, ParamInfo]:
         s = self.spec
         out: Dict[str, ParamInfo] = {s.embedding_name: ParamInfo((s.vocab_size, s.hidden_size))}
         for block, bspec in zip(self.blocks, s.blocks):
             for prefix, part in block.sub_parts().items():
                 for local, info in part.parameters().items():
-                    out[bspec.name + prefix + local] = info
+                    out[self._tensor_name(bspec.name + prefix, local)] = info
         for local, info in self.final_norm.parameters().items():
             out[s.final_norm_name + local] = info
         if s.head_name is not None:
@@ -73,7 +79,7 @@ class Model:
         for block, bspec in zip(self.blocks, s.blocks):
             for prefix, part in block.sub_parts().items():
                 full = bspec.name + prefix
-                part.load({local: tensors[full + local] for local in part.parameters()})
+                part.load({local: tensors[self._tensor_name(full, local)] for local in part.parameters()})
                 part.prepare(self.device, self.dtype)
         self.final_norm.load({local: tensors[s.final_norm_name + local] for local in self.final_norm.parameters()})
 

@@ -5,6 +5,10 @@ the chosen logits alone weighs the experts' outputs. Each expert is down(act(gat
 activation. The experts' matrices are stacked when they are loaded ([experts, 2 ff, hidden] and [experts, hidden, ff]); a
 step routes, groups its (row, choice) pairs by expert on the device, runs the two grouped products and sums a row's
 choices in a fixed order (csrc/moe.cu). Nothing of a step's routing is read on the host.
+
+``routing`` "table": there is no router; an integer table [vocab, top] gives every token id its experts (the entries of a
+row differ), each weighted 1 / top. ``shared``: one more expert of the same form that every row uses; its result (float32)
+is added by the kernel that sums a row's choices.
 """
 from __future__ import annotations
 
@@ -14,7 +18,7 @@ import torch
 
 from ..kernels import ops
 from .base import FeedForward
-from .registry import register_feed_forward
+from .registry import build_feed_forward, register_feed_forward
 from .spec import ParamInfo, RoutedExpertsSpec
 
 
@@ -27,8 +31,15 @@ class RoutedExperts(FeedForward):
         s = spec
         if not 0 < s.top <= s.experts or s.top > 32 or s.intermediate_size <= 0:
             raise ValueError(f"routed_experts: {s.top} of {s.experts} experts (at most 32 a row), ff {s.intermediate_size}")
-        if s.activation != "swiglu_clamp":
-            raise ops.KernelError(f"routed_experts: activation {s.activation!r} has no kernel (known: swiglu_clamp)")
+        ops.glu_code(s.activation)          # refuses a name no kernel knows
+        if s.routing not in ("softmax_top", "table"):
+            raise ValueError(f"routed_experts: routing must be 'softmax_top' or 'table', got {s.routing!r}")
+        if s.routing == "table" and s.vocab_size <= 0:
+            raise ValueError("routed_experts: routing by a table needs the vocabulary's size")
+        self.shared = build_feed_forward(s.shared) if s.shared is not None else None
+        if self.shared is not None and not getattr(self.shared, "takes_out_dtype", False):
+            raise ValueError("routed_experts: the shared expert must be able to return float32")
+        self.table: Optional[torch.Tensor] = None
         self.w_router: Optional[torch.Tensor] = None
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
@@ -41,17 +52,28 @@ class RoutedExperts(FeedForward):
     def parameters(self) -> Dict[str, ParamInfo]:
         s = self.spec
         W, F = s.hidden_size, s.intermediate_size
-        p = {s.router_name: ParamInfo((s.experts, W), ("normal", W ** -0.5))}
+        if s.routing == "table":
+            p = {s.table_name: ParamInfo((s.vocab_size, s.top), ("distinct_below", s.experts), integer=True)}
+        else:
+            p = {s.router_name: ParamInfo((s.experts, W), ("normal", W ** -0.5))}
         for e in range(s.experts):
             g, u, d = self._names(e)
             p[g] = ParamInfo((F, W), ("normal", W ** -0.5))
             p[u] = ParamInfo((F, W), ("normal", W ** -0.5))
             p[d] = ParamInfo((W, F), ("normal", F ** -0.5))
+        if self.shared is not None:
+            for local, info in self.shared.parameters().items():
+                p[s.shared_name + local] = info
         return p
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         s = self.spec
-        self.w_router = tensors[s.router_name].contiguous()
+        if s.routing == "table":
+            self.table = tensors[s.table_name].to(torch.int32).contiguous()
+        else:
+            self.w_router = tensors[s.router_name].contiguous()
+        if self.shared is not None:
+            self.shared.load({local: tensors[s.shared_name + local] for local in self.shared.parameters()})
         names = [self._names(e) for e in range(s.experts)]
         self.w_gate_up = torch.stack([torch.cat([tensors[g], tensors[u]], dim=0) for g, u, _ in names]).contiguous()
         self.w_down = torch.stack([tensors[d] for _, _, d in names]).contiguous()
@@ -60,6 +82,10 @@ class RoutedExperts(FeedForward):
         s = self.spec
         if not x.is_contiguous():
             x = x.contiguous()
-        routing = ops.moe_route(x, self.w_router, s.top)
-        out = ops.moe_experts(x, self.w_gate_up, self.w_down, routing, s.limit)
+        if s.routing == "table":
+            routing = ops.moe_route_table(ctx.token_ids, self.table, s.experts)
+        else:
+            routing = ops.moe_route(x, self.w_router, s.top)
+        add = self.shared.forward(x, ctx, out_dtype=torch.float32) if self.shared is not None else None
+        out = ops.moe_experts(x, self.w_gate_up, self.w_down, routing, s.limit, act=s.activation, add=add)
         return out if out_dtype in (None, torch.float32) else out.to(out_dtype)

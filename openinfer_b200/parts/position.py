@@ -37,10 +37,29 @@ class RotaryEncoding(PositionEncoding):
 
     def rotation_tables(self, device: torch.device):
         s = self.spec
-        key = (s.rotary_dim, float(s.theta), s.max_positions, s.scaling, s.precise, str(device))
+        key = (s.rotary_dim, float(s.theta), s.max_positions, s.scaling, s.precise, s.yarn, str(device))
         if key not in _TABLES:
             half = s.rotary_dim // 2
-            if s.scaling is None and not s.precise:
+            amplitude = 1.0
+            if s.yarn is not None:
+                # frequencies mixed between f and f / factor by a ramp over the pair index, whose ends are the pairs that
+                # make ``fast`` and ``slow`` turns within ``original`` positions; cos and sin scaled by 0.1 ln(factor) + 1
+                if s.scaling is not None:
+                    raise ValueError("a rotary encoding takes one way of stretching its waves, not two")
+                factor, original, fast, slow = (float(v) for v in s.yarn)
+                idx = torch.arange(half, dtype=torch.float64)
+                f = float(s.theta) ** (-2.0 * idx / s.rotary_dim)
+
+                def turns(t: float) -> float:
+                    return s.rotary_dim * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(float(s.theta)))
+
+                lo = max(math.floor(turns(fast)), 0)
+                hi = min(math.ceil(turns(slow)), s.rotary_dim - 1)
+                ramp = torch.clamp((idx - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+                f = f / factor * ramp + f * (1.0 - ramp)
+                amplitude = 0.1 * math.log(factor) + 1.0
+                ang = torch.arange(s.max_positions, dtype=torch.float64)[:, None] * f[None, :]
+            elif s.scaling is None and not s.precise:
                 idx = torch.arange(half, dtype=torch.float32)
                 inv_freq = 1.0 / torch.pow(torch.tensor(float(s.theta), dtype=torch.float32),
                                            idx * 2.0 / s.rotary_dim)
@@ -55,8 +74,8 @@ class RotaryEncoding(PositionEncoding):
                 t = (original / wave - low) / (high - low) if high != low else torch.zeros_like(wave)
                 f = torch.where(wave < original / high, f, torch.where(wave > original / low, f / factor, (1.0 - t) * f / factor + t * f))
                 ang = torch.arange(s.max_positions, dtype=torch.float64)[:, None] * f[None, :]
-            _TABLES[key] = (torch.cos(ang).to(torch.float32).contiguous().to(device),
-                            torch.sin(ang).to(torch.float32).contiguous().to(device))
+            _TABLES[key] = ((torch.cos(ang) * amplitude).to(torch.float32).contiguous().to(device),
+                            (torch.sin(ang) * amplitude).to(torch.float32).contiguous().to(device))
         return _TABLES[key]
 
 

@@ -50,6 +50,11 @@ class PositionSpec:
     # s = (original / l - low) / (high - low)
     scaling: Optional[Tuple[float, float, float, float]] = None
     precise: bool = False       # frequencies and angles in float64 (cos and sin rounded once); False: float32 throughout
+    # another way to stretch the waves ("YaRN"), (factor, original, fast, slow): with turns(t) = rotary_dim ln(original /
+    # (2 pi t)) / (2 ln theta), lo = max(floor(turns(fast)), 0), hi = min(ceil(turns(slow)), rotary_dim - 1) and
+    # r_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), frequency i becomes r_i f_i / factor + (1 - r_i) f_i, and cos and
+    # sin are both multiplied by 0.1 ln(factor) + 1. Tables in float64, rounded once.
+    yarn: Optional[Tuple[float, float, float, float]] = None
 
 
 @dataclasses.dataclass(frozen=True)
@@ -73,6 +78,20 @@ class AttentionSpec:
     o_name: str = "o_proj.weight"
     q_norm_name: str = "q_norm.weight"
     k_norm_name: str = "k_norm.weight"
+    # a short causal filter over time on every channel of q, k and v, directly behind the projections (no bias, no
+    # activation): ``conv_taps`` taps, tensors q_name / k_name / v_name + ``conv_suffix`` of shape [channels, taps]; the last
+    # taps - 1 projected rows of a request are state
+    conv_taps: int = 0
+    conv_suffix: str = ".conv"
+    # the query at position p is multiplied by 1 + coef * ln(floor((p + 1) / every) + 1): (coef, every)
+    q_temperature: Optional[Tuple[float, int]] = None
+    score_cap: float = 0.0                  # > 0: score <- cap * tanh(score / cap)
+    # > 0: head h (of H) takes 2^(-e (h + 1) / H) * (i - j) off the score of key j for query i, e this exponent
+    distance_slope_exponent: float = 0.0
+    sink: bool = False                      # a learned number per head in the softmax's denominator (``sink_name`` [heads])
+    sink_name: str = "sink"
+    head_gate: bool = False                 # head h's output is multiplied by sigmoid(W_g x)_h (``gate_name`` [heads, hidden])
+    gate_name: str = "g"
 
 
 @dataclasses.dataclass(frozen=True)
@@ -101,6 +120,16 @@ class LatentAttentionSpec:
     up_v_name: str = "uv"
     gate_name: str = "g"
     out_name: str = "o"
+    # a rotated part beside the latent: every head's query has ``rope_dim`` more numbers behind its ``qk_dim`` unrotated
+    # ones, the down-projection ``rope_dim`` more rows behind the latent's (one key part shared by all heads, not normed);
+    # both are turned by ``position`` and their dot product is added to the score. The cached row is [latent, key part].
+    rope_dim: int = 0
+    position: Optional[PositionSpec] = None
+    sink: bool = False                      # a learned number per head in the softmax's denominator (``sink_name`` [heads])
+    sink_name: str = "sink"
+    # "head": one gate per head (``gate_name`` [heads, hidden]); "element": one per output number ([heads * v_dim, hidden]),
+    # which sits between the value up-projection and the output projection, so the values' up-projection runs in every step
+    gate_per: str = "head"
 
 
 @dataclasses.dataclass(frozen=True)
@@ -135,6 +164,25 @@ class DepthAverageSpec:
     kind: str = "depth_average"
     terms: int = 0
     param_name: str = ""
+
+
+@dataclasses.dataclass(frozen=True)
+class TokenInputSpec:
+    """A per-layer input that depends on the token id alone: y = proj (gelu_tanh(gate x) * e) with e the ``dim`` numbers
+    at ``offset`` of the token's row in a table shared by all layers (``table_name``, an absolute tensor name,
+    [vocab_size, table_width]); the stream takes x + rms(y) * weight."""
+
+    kind: str = "token_input"
+    hidden_size: int = 0
+    dim: int = 0
+    offset: int = 0
+    vocab_size: int = 0
+    table_width: int = 0
+    eps: float = 1e-6
+    table_name: str = "/side.embed"          # a leading "/" makes a tensor name absolute (no block or part prefix)
+    gate_name: str = "gate"
+    proj_name: str = "proj"
+    norm_name: str = "norm"
 
 
 @dataclasses.dataclass(frozen=True)
@@ -178,6 +226,14 @@ class RoutedExpertsSpec:
     gate_name: str = "gate"
     up_name: str = "up"
     down_name: str = "down"
+    # "softmax_top": the ``top`` largest router logits, weighted by their softmax. "table": no router; an integer tensor
+    # ``table_name`` [vocab_size, top] gives every token id its experts, each weighted 1 / top
+    routing: str = "softmax_top"
+    table_name: str = "table"
+    vocab_size: int = 0
+    # an expert of the same form that every row uses, added to the routed sum (a GatedMlpSpec; tensors under ``shared_name``)
+    shared: Any = None
+    shared_name: str = "shared."
 
 
 @dataclasses.dataclass(frozen=True)
@@ -249,6 +305,8 @@ class BlockSpec:
     stream_coefficients: bool = False
     mixer_streams_name: str = "hc1."
     feed_forward_streams_name: str = "hc2."
+    token_input: Any = None                      # blocks that end with a per-token input (TokenInputSpec)
+    token_input_name: str = "side."
 
 
 @dataclasses.dataclass(frozen=True)

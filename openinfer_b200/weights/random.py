@@ -33,7 +33,12 @@ def random_tensors(expected: Dict[str, ParamInfo], seed: int, dtype: torch.dtype
         gen = torch.Generator(device=device)
         gen.manual_seed(_tensor_seed(seed, name))
         if info.integer:
-            out[name] = torch.randint(0, 2, info.shape, generator=gen, device=device, dtype=torch.int32)
+            if info.init[0] == "distinct_below":     # ("distinct_below", n): every row holds different numbers below n
+                rows = [torch.randperm(int(info.init[1]), generator=gen, device=device)[: info.shape[-1]]
+                        for _ in range(int(torch.tensor(info.shape[:-1]).prod()))]
+                out[name] = torch.stack(rows).reshape(info.shape).to(torch.int32)
+            else:
+                out[name] = torch.randint(0, 2, info.shape, generator=gen, device=device, dtype=torch.int32)
             continue
         kind, std = info.init[0], info.init[1]
         t = torch.randn(info.shape, generator=gen, device=device, dtype=torch.float32) * std
