@@ -21,7 +21,9 @@ exits with 2.
 ``--design delunex`` measures something else and leaves the above as it is: the Delunex design at layer sizes of
 real models beside Qwen3 at equal sizes (decode at batch 1 / 8 / 64, a 2,048-token prefill, with ``--design-kernels``
 every kernel's time per step), one JSON line of its own. ``--design pilonex`` does the same for the Pilonex design
-(hyper-connection streams, windowed attention beside a gated delta rule, matrix memories, dense and routed feed-forwards).
+(hyper-connection streams, windowed attention beside a gated delta rule, matrix memories, dense and routed feed-forwards),
+``--design bubalix`` for the Bubalix design (filtered, capped, windowed attention with sinks and latent attention with a
+rotated key part under one norm with experts picked by a token table, a shared expert and a side input per token).
 """
 from __future__ import annotations
 
@@ -461,6 +463,27 @@ def pilonex_configs(key, layers=None):
     return pilonex, design_configs(key, layers)[1]
 
 
+def bubalix_configs(key, layers=None):
+    """Bubalix at the same widths and depths: of every four layers three are "attention" (windowed grouped-query attention
+    with per head 128 keys and values, a quarter as many kv heads, four-tap filters on q, k and v, query temperature, capped
+    scores, distance slopes, sinks and head gates) and one is "latent_attention" (a latent of 96 numbers and a rotated key
+    part of 32 in one cached row of 128, per head 128 unrotated query numbers and values, stretched waves, a sink and a gate
+    per output number); every layer has sixteen experts of a quarter of Qwen3's feed-forward of which the token id picks two,
+    an expert of half its size that every token uses, and a side input of 64 numbers. Qwen3 as in ``design_configs``."""
+    width, n_layers, heads, window, _, inter = DESIGN_SIZES[key]
+    n_layers = layers or n_layers
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window},
+           "conv": 4, "q_temp": {"coef": 0.5, "every": 1024}, "softcap": 30.0}
+    lat = {"heads": heads, "dim": 128, "rot_dim": 32, "vdim": 128, "kv_rank": 96, "scale": 160 ** -0.5,
+           "rot": {"dims": 32, "base": 500000.0, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    mlp = {"kind": "moe", "expert": {"ff": inter // 4}, "router": {"experts": 16, "top": 2}, "shared": {"ff": inter // 2}}
+    lay = [{"type": "latent_attention" if i % 4 == 1 else "attention", "mixer": dict(lat if i % 4 == 1 else att), "mlp": dict(mlp)}
+           for i in range(n_layers)]
+    bubalix = {"architecture": "Bubalix", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "embedding": {"scale": 1.0},
+               "token_side": {"dim": 64}, "layers": lay}
+    return bubalix, design_configs(key, layers)[1]
+
+
 def _part_tensors(torch, part, seen=None):
     """Every tensor a part holds, the tensors of parts inside it included."""
     seen = set() if seen is None else seen
@@ -571,6 +594,8 @@ class DesignBench:
             for part in block.sub_parts().values():
                 for t in _part_tensors(self.torch, part, seen):
                     share = 1.0
+                    if t is getattr(part, "table", None):          # a table indexed by the token id: one row a token
+                        share = min(1.0, batch / t.shape[0])
                     if t.dim() == 3 and hasattr(part, "spec") and getattr(part.spec, "experts", 0):
                         share = min(1.0, batch * part.spec.top / part.spec.experts)
                     total += int(t.numel() * t.element_size() * share)
@@ -637,7 +662,7 @@ def design_mode(args, torch, mods, peaks, peaks_src):
             if key not in DESIGN_SIZES:
                 raise SystemExit(f"--design-sizes: unknown size {key!r} (known: {', '.join(DESIGN_SIZES)})")
             rec = {"width": DESIGN_SIZES[key][0], "layers": args.layers or DESIGN_SIZES[key][1]}
-            configs = pilonex_configs(key, args.layers) if args.design == "pilonex" else design_configs(key, args.layers)
+            configs = {"pilonex": pilonex_configs, "bubalix": bubalix_configs}.get(args.design, design_configs)(key, args.layers)
             for arch, cfg in zip((args.design, "qwen3"), configs):
                 b = DesignBench(torch, mods, cfg, args.dtype, CONTEXT, 64, steps + warm + 16)
                 r = {"weights_gb": round(b.runner.model.weight_bytes() / 1e9, 3)}
@@ -698,7 +723,7 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill", "mixed", "sampler"], default=None,
                     help="run warm-up, then ONE step between cudaProfilerStart/Stop and exit "
                          "(for `ncu --profile-from-start off`); prints no benchmark line")
-    ap.add_argument("--design", default=None, choices=["delunex", "pilonex"],
+    ap.add_argument("--design", default=None, choices=["delunex", "pilonex", "bubalix"],
                     help="instead of the headline workload: this design at layer sizes of real models beside Qwen3 at equal "
                          "sizes (decode at batch 1/8/64, a 2,048-token prefill), one JSON line")
     ap.add_argument("--design-sizes", default=None, help="sizes for --design, comma separated (1k, 2k, 4k; default 1k,2k)")

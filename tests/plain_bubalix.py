@@ -62,6 +62,28 @@ def query_temperature(T: int, coef: float, every: int, dtype) -> torch.Tensor:
     return 1.0 + coef * torch.log(torch.floor((p + 1.0) / every) + 1.0)
 
 
+def scored_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: Optional[int], sink: torch.Tensor,
+                     cap: Optional[float] = None, slopes: Optional[torch.Tensor] = None, temperature: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """q [T, H, D], k [T, G, D], v [T, G, V] of one sequence -> [T, H, V]. Head h reads key/value head h // (H / G). The
+    score of (i, j) is (t_i q_i . k_j) * scale, capped as cap * tanh(s / cap), minus slope_h * (i - j); keys j <= i within the
+    window; the softmax's denominator holds exp(sink_h) as well."""
+    T, H, G = q.shape[0], q.shape[1], k.shape[1]
+    if temperature is not None:
+        q = q * temperature[:, None, None]
+    seen = visibility(T, window)
+    dist = (torch.arange(T)[:, None] - torch.arange(T)[None, :]).to(q.dtype)
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    for head in range(H):
+        g = head // (H // G)
+        s = (q[:, head] @ k[:, g].T) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        if slopes is not None:
+            s = s - slopes[head] * dist
+        out[:, head] = softmax_with_sink(s, seen, sink[head]) @ v[:, g]
+    return out
+
+
 def attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict) -> torch.Tensor:
     """Grouped-query attention without rotation: filtered q, k, v; a temperature on q; capped scores; a distance bias;
     a window; a sink; one gate per head."""
@@ -70,20 +92,9 @@ def attention(h: torch.Tensor, W: Dict[str, torch.Tensor], p: str, m: dict) -> t
     q, k, v = h @ W[p + "q"].T, h @ W[p + "k"].T, h @ W[p + "v"].T
     if m.get("conv"):
         q, k, v = time_filter(q, W[p + "q.conv"]), time_filter(k, W[p + "k.conv"]), time_filter(v, W[p + "v.conv"])
-    if m.get("q_temp"):
-        q = q * query_temperature(T, m["q_temp"]["coef"], m["q_temp"]["every"], h.dtype)[:, None]
-    q, k, v = q.view(T, H, D), k.view(T, G, D), v.view(T, G, V)
-    seen = visibility(T, m["mask"]["size"] if m.get("mask") else None)
-    dist = (torch.arange(T)[:, None] - torch.arange(T)[None, :]).to(h.dtype)
-    slopes = distance_slopes(H, h.dtype)
-    out = torch.zeros(T, H, V, dtype=h.dtype)
-    for head in range(H):
-        g = head // (H // G)
-        s = (q[:, head] @ k[:, g].T) * m["scale"]
-        if m.get("softcap"):
-            s = m["softcap"] * torch.tanh(s / m["softcap"])
-        s = s - slopes[head] * dist
-        out[:, head] = softmax_with_sink(s, seen, W[p + "sink"][head]) @ v[:, g]
+    temperature = query_temperature(T, m["q_temp"]["coef"], m["q_temp"]["every"], h.dtype) if m.get("q_temp") else None
+    out = scored_attention(q.view(T, H, D), k.view(T, G, D), v.view(T, G, V), m["scale"], m["mask"]["size"] if m.get("mask") else None,
+                           W[p + "sink"], m.get("softcap"), distance_slopes(H, h.dtype), temperature)
     out = out * torch.sigmoid(h @ W[p + "g"].T)[:, :, None]
     return out.reshape(T, H * V) @ W[p + "o"].T
 
