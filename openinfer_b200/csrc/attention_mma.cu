@@ -45,7 +45,11 @@ struct AttnParams {
   const void* q_norm_w; const void* k_norm_w; int norm_dtype; float eps, w_offset;
   const float* cos_tab; const float* sin_tab; int rot_half, max_pos;
   const int* positions; const int* slots;
+  // kernels instantiated with MODS: the layer's changes to its scores (a sink, distance slopes, a cap, a query
+  // temperature) and the softmax scale itself (scale_log2 without the factor log2(e))
+  OiScoreMods mods; float scale;
 };
+
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) {
   return (unsigned)__cvta_generic_to_shared(p);
@@ -118,7 +122,7 @@ __device__ __forceinline__ void load_tile(bf16* smem, const bf16* cache, const A
 // MT: 16-row slabs per warp. MT = 2 (128 rows per CTA) lets every K/V fragment read from shared
 // memory feed two MMAs, which halves the shared-memory traffic per flop: the version for prompt
 // portions. MT = 1 (64 rows per CTA) wastes less on short portions.
-template <int HD, int MT>
+template <int HD, int MT, bool MODS>
 __global__ void __launch_bounds__(kThreads)
 attention_mma_kernel(const AttnParams p) {
   pdl_start();
@@ -199,6 +203,24 @@ attention_mma_kernel(const AttnParams p) {
   float m[MT][2], l[MT][2];
 #pragma unroll
   for (int mt = 0; mt < MT; ++mt) { m[mt][0] = m[mt][1] = -INFINITY; l[mt][0] = l[mt][1] = 0.f; }
+  // MODS: the scores are brought into their final form (units of log2) before the softmax, which then runs with scale 1;
+  // the sink enters as a first term exp(sink) of the row's sum, in the slice that holds the row's first keys
+  const float sl2 = MODS ? 1.f : p.scale_log2;
+  RowMods rm[MT][2];
+  if (MODS) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        const int r = warp_row0 + mt * 16 + (lane >> 2) + 8 * i;
+        const int head = kvh * group + r % group;
+        rm[mt][i].init(p.mods, p.scale, head, pos[mt][i]);
+        if (p.mods.sinks && split == 0) {
+          m[mt][i] = p.mods.sinks[head] * kLog2e;
+          l[mt][i] = (lane & 3) == 0 ? 1.f : 0.f;      // the row's sum is spread over four lanes
+        }
+      }
+  }
 
   // ldmatrix lane constants (element offsets; chunk indices enter through one XOR)
   const int lm_mat = lane >> 3, lm_rin = lane & 7;
@@ -275,6 +297,17 @@ attention_mma_kernel(const AttnParams p) {
       // ---- mask (only where a row may not see the whole tile) + online softmax
       const bool full = key0 + kKeys - 1 <= warp_first_pos && (p.window <= 0 || key0 > warp_last_pos - p.window) &&
                         warp_row0 + 16 * MT <= tile_toks * group;
+      if (MODS) {
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int j = 0; j < kKeys / 8; ++j)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
+              s[mt][j][e] = rm[mt][e >> 1].apply(s[mt][j][e], pos[mt][e >> 1] - key);
+            }
+      }
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         // the running maximum m is kept of the RAW scores; the scale enters in one fused
@@ -302,15 +335,15 @@ attention_mma_kernel(const AttnParams p) {
         for (int i = 0; i < 2; ++i) {
           m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 1));
           m_new[i] = fmaxf(m_new[i], __shfl_xor_sync(0xffffffffu, m_new[i], 2));
-          corr[i] = (m[mt][i] == -INFINITY) ? 0.f : fast_exp2((m[mt][i] - m_new[i]) * p.scale_log2);
+          corr[i] = (m[mt][i] == -INFINITY) ? 0.f : fast_exp2((m[mt][i] - m_new[i]) * sl2);
           l[mt][i] *= corr[i];
-          base[i] = m_new[i] == -INFINITY ? 0.f : m_new[i] * p.scale_log2;
+          base[i] = m_new[i] == -INFINITY ? 0.f : m_new[i] * sl2;
           m[mt][i] = m_new[i];
         }
 #pragma unroll
         for (int j = 0; j < kKeys / 8; ++j) {
-          const float p0 = fast_exp2(fmaf(s[mt][j][0], p.scale_log2, -base[0])), p1 = fast_exp2(fmaf(s[mt][j][1], p.scale_log2, -base[0]));
-          const float p2 = fast_exp2(fmaf(s[mt][j][2], p.scale_log2, -base[1])), p3 = fast_exp2(fmaf(s[mt][j][3], p.scale_log2, -base[1]));
+          const float p0 = fast_exp2(fmaf(s[mt][j][0], sl2, -base[0])), p1 = fast_exp2(fmaf(s[mt][j][1], sl2, -base[0]));
+          const float p2 = fast_exp2(fmaf(s[mt][j][2], sl2, -base[1])), p3 = fast_exp2(fmaf(s[mt][j][3], sl2, -base[1]));
           l[mt][0] += p0 + p1;
           l[mt][1] += p2 + p3;
           // accumulator tiles (2i, 2i+1) are the A fragment of key step i
@@ -375,7 +408,7 @@ attention_mma_kernel(const AttnParams p) {
 #pragma unroll
         for (int j = 0; j < kOTiles; ++j)
           *reinterpret_cast<float2*>(op + j * 8) = make_float2(o[mt][j][2 * i] * inv, o[mt][j][2 * i + 1] * inv);
-        if ((lane & 3) == 0) p.part_lse[slot] = li > 0.f ? m[mt][i] * p.scale_log2 + log2f(li) : -INFINITY;  // base-2 log-sum-exp
+        if ((lane & 3) == 0) p.part_lse[slot] = li > 0.f ? m[mt][i] * sl2 + log2f(li) : -INFINITY;  // base-2 log-sum-exp
       }
     }
   }
@@ -522,7 +555,7 @@ __device__ __forceinline__ void warp_norm_rope_head(const bf16* __restrict__ src
   head_finish(head_load(src, rot_half, lane), src, dst, hd, w, norm_dtype, eps, w_offset, wa, wb, c, sn, rot_half, lane);
 }
 
-template <int HD>
+template <int HD, bool MODS>
 __global__ void __launch_bounds__(kDecWarps * 32)
 attention_decode_kernel(const AttnParams p) {
   pdl_trigger();
@@ -567,6 +600,20 @@ attention_decode_kernel(const AttnParams p) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) o[j][e] = 0.f;
   float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  // MODS: the scores take their final form before the softmax; the sink is the first term of the sum of the row's slice 0
+  RowMods rm[2];
+  if (MODS) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int r = (lane >> 2) + 8 * i;
+      const int head = kvh * group + (r < group ? r : 0);
+      rm[i].init(p.mods, p.scale, head, pos);
+      if (p.mods.sinks && split == 0 && r < group) {
+        m[i] = p.mods.sinks[head] * kLog2e;
+        l[i] = (lane & 3) == 0 ? 1.f : 0.f;
+      }
+    }
+  }
 
   // the next tile to copy: its first key, its page (index into the block table) and offset there
   const long long v_delta = p.v_cache - p.k_cache;
@@ -710,12 +757,20 @@ attention_decode_kernel(const AttnParams p) {
       // a tile whose every key every row sees needs no mask (rows beyond the group hold zeros
       // and are never stored)
       const bool full = key0 + kDecKeys <= kv_len && (p.window <= 0 || key0 > pos - p.window);
+      const float sl2 = MODS ? 1.f : p.scale_log2;
+      if (MODS) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            s[j][e] = rm[e >> 1].apply(s[j][e], pos - (key0 + j * 8 + (lane & 3) * 2 + (e & 1)));
+      }
       if (full) {
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
-            s[j][e] *= p.scale_log2;
+            s[j][e] *= sl2;
             m_new[e >> 1] = fmaxf(m_new[e >> 1], s[j][e]);
           }
         }
@@ -727,7 +782,7 @@ attention_decode_kernel(const AttnParams p) {
             const int i = e >> 1;
             const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
             const bool ok = key <= pos && (p.window <= 0 || key > pos - p.window);
-            s[j][e] = ok ? s[j][e] * p.scale_log2 : -INFINITY;
+            s[j][e] = ok ? s[j][e] * sl2 : -INFINITY;
             m_new[i] = fmaxf(m_new[i], s[j][e]);
           }
         }
@@ -959,23 +1014,28 @@ __global__ void attention_merge_kernel(bf16* __restrict__ out, int out_row_strid
   for (int e = 0; e < kPer; ++e) dst[e] = __float2bfloat16_rn(acc[e] * inv);
 }
 
-template <int HD, int MT>
+template <int HD, int MT, bool MODS>
 int launch_tiles(const AttnParams& p, int num_items, cudaStream_t s) {
   constexpr int smem = (64 * MT + 4 * kKeys) * HD * (int)sizeof(bf16);
   static bool configured = false;
   if (!configured) {
-    OI_CHECK_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    OI_CHECK_CUDA(cudaFuncSetAttribute(attention_mma_kernel<HD, MT, MODS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
-  oi_launch(attention_mma_kernel<HD, MT>, (unsigned)((long long)num_items * p.nkv), kThreads, smem, s, p);
+  oi_launch(attention_mma_kernel<HD, MT, MODS>, (unsigned)((long long)num_items * p.nkv), kThreads, smem, s, p);
   OI_CHECK_LAUNCH();
   return OI_OK;
+}
+
+bool has_mods(const AttnParams& p) {
+  return p.mods.sinks || p.mods.slopes || p.mods.softcap > 0.f || p.mods.qt_every > 0;
 }
 
 template <int HD>
 int launch(const AttnParams& p, int num_items, const int* row_splits, int tokens, int any_split, int rows_per_cta,
            cudaStream_t s) {
-  const int rc = rows_per_cta == 128 ? launch_tiles<HD, 2>(p, num_items, s) : launch_tiles<HD, 1>(p, num_items, s);
+  const int rc = has_mods(p) ? (rows_per_cta == 128 ? launch_tiles<HD, 2, true>(p, num_items, s) : launch_tiles<HD, 1, true>(p, num_items, s))
+                             : (rows_per_cta == 128 ? launch_tiles<HD, 2, false>(p, num_items, s) : launch_tiles<HD, 1, false>(p, num_items, s));
   if (rc) return rc;
   if (any_split) {
     const long long warps = (long long)tokens * p.nq;
@@ -996,15 +1056,15 @@ int launch_merge(void* out, int out_row_stride, const float* part_o, const float
   return OI_OK;
 }
 
-template <int HD>
-int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int tokens, cudaStream_t s) {
+template <int HD, bool MODS>
+int launch_decode_as(const AttnParams& p, int num_items, const int* row_splits, int tokens, cudaStream_t s) {
   // the warps' rings, room for the rotated query heads of one kv head and the step's key and value
   // (fuse_rope), and the receive buffer of the merge by deposit
   constexpr int kRecvMax = 12 * 1024;
   constexpr int smem = (kDecWarps * kDecStages * 2 * kDecKeys + 18) * HD * (int)sizeof(bf16) + kRecvMax;
   static bool configured = false;
   if (!configured) {
-    OI_CHECK_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    OI_CHECK_CUDA(cudaFuncSetAttribute(attention_decode_kernel<HD, MODS>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     configured = true;
   }
   dim3 grid(num_items, p.nkv);
@@ -1014,17 +1074,23 @@ int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int
     const int passes = (p.group * HD + 128 * csize - 1) / (128 * csize);
     AttnParams q = p;
     q.merge_in_kernel = (csize > 1 && (passes * p.max_splits * 128 + p.max_splits * 16) * 4 <= kRecvMax) ? 2 : 1;
-    oi_launch_cluster(attention_decode_kernel<HD>, grid, kDecWarps * 32, smem, s, csize, q);
+    oi_launch_cluster(attention_decode_kernel<HD, MODS>, grid, kDecWarps * 32, smem, s, csize, q);
     OI_CHECK_LAUNCH();
     return OI_OK;
   }
-  oi_launch(attention_decode_kernel<HD>, grid, kDecWarps * 32, smem, s, p);
+  oi_launch(attention_decode_kernel<HD, MODS>, grid, kDecWarps * 32, smem, s, p);
   OI_CHECK_LAUNCH();
   const long long warps = (long long)tokens * p.nq;
   oi_launch(attention_merge_kernel<HD>, (unsigned)((warps + 3) / 4), 128, 0, s,
       p.out, p.out_row_stride, p.part_o, p.part_lse, row_splits, p.nq, p.max_splits, tokens);
   OI_CHECK_LAUNCH();
   return OI_OK;
+}
+
+template <int HD>
+int launch_decode(const AttnParams& p, int num_items, const int* row_splits, int tokens, cudaStream_t s) {
+  return has_mods(p) ? launch_decode_as<HD, true>(p, num_items, row_splits, tokens, s)
+                     : launch_decode_as<HD, false>(p, num_items, row_splits, tokens, s);
 }
 
 }  // namespace
@@ -1041,7 +1107,7 @@ int decode_entry(const void* q, int q_row_stride, void* out, int out_row_stride,
                  int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
                  int num_items, const int* row_splits, int tokens, int nq, int nkv, int hd,
                  float scale, int window, float* part_o, float* part_lse, int max_splits,
-                 int merge_in_kernel, const RopeArgs* rope, void* stream) {
+                 int merge_in_kernel, const RopeArgs* rope, const OiScoreMods* mods, void* stream) {
   OI_REQUIRE(hd == 32 || hd == 64 || hd == 128, "attention_decode: head_dim %d not covered (32, 64 or 128)", hd);
   OI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq / nkv <= 16, "attention_decode: group %d/%d not covered (<= 16)", nq, nkv);
   OI_REQUIRE(q_row_stride % 2 == 0 && page_stride % 8 == 0, "attention_decode: misaligned strides");
@@ -1069,6 +1135,10 @@ int decode_entry(const void* q, int q_row_stride, void* out, int out_row_stride,
   p.part_o = part_o; p.part_lse = part_lse; p.max_splits = max_splits;
   p.merge_in_kernel = merge_in_kernel ? 1 : 0;
   p.fuse_rope = 0;
+  p.mods = OiScoreMods{};
+  if (mods) p.mods = *mods;
+  p.scale = scale;
+  OI_REQUIRE(!(rope && has_mods(p)), "attention_decode: modified scores and the fused rotation do not come together");
   if (rope) {
     OI_REQUIRE(rope->rot_half > 0 && rope->rot_half % 2 == 0 && 2 * rope->rot_half <= hd && rope->cos_tab && rope->sin_tab &&
                    rope->max_pos > 0 && rope->positions,
@@ -1105,7 +1175,19 @@ OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int o
                                int merge_in_kernel, void* stream) {
   return decode_entry(q, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, block_table, bt_stride,
                       cu_seqlens, kv_lens, items, num_items, row_splits, tokens, nq, nkv, hd, scale, window, part_o, part_lse,
-                      max_splits, merge_in_kernel, nullptr, stream);
+                      max_splits, merge_in_kernel, nullptr, nullptr, stream);
+}
+
+// oi_attention_decode for a layer that modifies its scores (`mods`: sink, distance slopes, cap, query temperature).
+OI_API int oi_attention_decode_mods(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
+                                    const void* v_cache, long long page_stride, int page_size, const int* block_table,
+                                    int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
+                                    int num_items, const int* row_splits, int tokens, int nq, int nkv, int hd,
+                                    float scale, int window, float* part_o, float* part_lse, int max_splits,
+                                    int merge_in_kernel, const OiScoreMods* mods, void* stream) {
+  return decode_entry(q, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, block_table, bt_stride,
+                      cu_seqlens, kv_lens, items, num_items, row_splits, tokens, nq, nkv, hd, scale, window, part_o, part_lse,
+                      max_splits, merge_in_kernel, nullptr, mods, stream);
 }
 
 // The same with the per-head q/k norm, the rotation and the write of the step's key and value fused in:
@@ -1123,7 +1205,7 @@ OI_API int oi_attention_decode_rope(const void* qkv, int q_row_stride, void* out
   RopeArgs r{q_norm_w, k_norm_w, norm_dtype, eps, w_offset, cos_tab, sin_tab, rot_half, max_pos, positions, slots, write_kv};
   return decode_entry(qkv, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, block_table, bt_stride,
                       cu_seqlens, kv_lens, items, num_items, row_splits, tokens, nq, nkv, hd, scale, window, part_o, part_lse,
-                      max_splits, merge_in_kernel, &r, stream);
+                      max_splits, merge_in_kernel, &r, nullptr, stream);
 }
 
 // items: int32 [num_items, 4] = (request, first token of the tile, split, nsplits), planned by the
@@ -1136,6 +1218,18 @@ OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_
                             int num_items, const int* row_splits, int tokens, int any_split, int nq, int nkv,
                             int hd, float scale, int window, float* part_o, float* part_lse, int max_splits,
                             int rows_per_cta, void* stream) {
+  return oi_attention_mma_mods(q, q_row_stride, out, out_row_stride, k_cache, v_cache, page_stride, page_size, block_table,
+                               bt_stride, cu_seqlens, kv_lens, items, num_items, row_splits, tokens, any_split, nq, nkv, hd,
+                               scale, window, part_o, part_lse, max_splits, rows_per_cta, nullptr, stream);
+}
+
+// The same for a layer that modifies its scores (`mods`: sink, distance slopes, cap, query temperature; null: none).
+OI_API int oi_attention_mma_mods(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
+                                 const void* v_cache, long long page_stride, int page_size, const int* block_table,
+                                 int bt_stride, const int* cu_seqlens, const int* kv_lens, const int* items,
+                                 int num_items, const int* row_splits, int tokens, int any_split, int nq, int nkv,
+                                 int hd, float scale, int window, float* part_o, float* part_lse, int max_splits,
+                                 int rows_per_cta, const OiScoreMods* mods, void* stream) {
   OI_REQUIRE(rows_per_cta == 64 || rows_per_cta == 128, "attention_mma: rows_per_cta %d (64 or 128)", rows_per_cta);
   OI_REQUIRE(hd == 32 || hd == 64 || hd == 128, "attention_mma: head_dim %d not covered (32, 64 or 128)", hd);
   OI_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0 && nq / nkv <= rows_per_cta, "attention_mma: bad head counts nq=%d nkv=%d", nq, nkv);
@@ -1158,6 +1252,9 @@ OI_API int oi_attention_mma(const void* q, int q_row_stride, void* out, int out_
   p.part_o = part_o; p.part_lse = part_lse; p.max_splits = max_splits;
   p.merge_in_kernel = 0;
   p.fuse_rope = 0;
+  p.mods = OiScoreMods{};
+  if (mods) p.mods = *mods;
+  p.scale = scale;
   cudaStream_t s = (cudaStream_t)stream;
   if (hd == 32) return launch<32>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);
   if (hd == 64) return launch<64>(p, num_items, row_splits, tokens, any_split, rows_per_cta, s);

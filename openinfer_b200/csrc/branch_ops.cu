@@ -295,7 +295,7 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(
     TO* __restrict__ out, const TX* __restrict__ x, const void* __restrict__ w, int w_dtype, float* __restrict__ state,
     long long state_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ token_req,
     const int* __restrict__ state_slots, const int* __restrict__ state_phase, int tokens, int channels, int taps, int add_input,
-    int conv_blocks) {
+    int conv_blocks, long long x_stride, long long out_stride, int act) {
   pdl_trigger();
   const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4;
   const int keep = taps - 1;
@@ -312,7 +312,7 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(
     for (int k = 0; k < keep; ++k) {
       const int s = n + k - keep;
       float v[4];
-      if (s >= 0) load4(x + (size_t)(start + s) * channels + c, v);
+      if (s >= 0) load4(x + (size_t)(start + s) * x_stride + c, v);
       else load4(old + (size_t)(k + n) * channels + c, v);
       store4(nx + (size_t)k * channels + c, v);
     }
@@ -335,7 +335,7 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(
 #pragma unroll
   for (int j = 0; j < kTaps; ++j) {
     const int r = t0 - 1 - j;
-    if (j < keep && r >= 0) load4(x + (size_t)r * channels + c, ring[j]);
+    if (j < keep && r >= 0) load4(x + (size_t)r * x_stride + c, ring[j]);
   }
   const int t_end = min(tokens, t0 + kConvRows);
   // The requests of the rows and of the taps - 1 rows above them, and the rows' inputs: all asked for before any is used.
@@ -349,7 +349,7 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(
   }
 #pragma unroll
   for (int i = 0; i < kConvRows; ++i)
-    if (t0 + i < t_end) load4(x + (size_t)(t0 + i) * channels + c, curs[i]);
+    if (t0 + i < t_end) load4(x + (size_t)(t0 + i) * x_stride + c, curs[i]);
 #pragma unroll
   for (int i = 0; i < kConvRows; ++i) {
     const int t = t0 + i;
@@ -384,7 +384,11 @@ __global__ void __launch_bounds__(256) short_conv_vec_kernel(
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[e] += wt[j][e] * v[e];
     }
-    store4(out + (size_t)t * channels + c, acc);
+    if (act == OI_ACT_SILU) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[e] = acc[e] / (1.f + expf(-acc[e]));
+    }
+    store4(out + (size_t)t * out_stride + c, acc);
 #pragma unroll
     for (int j = kTaps - 1; j > 0; --j) {
 #pragma unroll
@@ -529,8 +533,8 @@ OI_API int oi_short_conv_strided(void* out, int out_dtype, long long out_stride,
   cudaStream_t s = (cudaStream_t)stream;
   const int cy = (channels + kRowThreads - 1) / kRowThreads;
   const dim3 grid(tokens, cy);
-  const bool vec = act == OI_ACT_NONE && x_stride == channels && out_stride == channels && channels % 4 == 0 &&
-                   taps <= kConvMaxTaps && aligned16(out) && aligned16(x) &&
+  const bool vec = x_stride % 4 == 0 && out_stride % 4 == 0 && channels % 4 == 0 && taps <= kConvMaxTaps && aligned16(out) &&
+                   aligned16(x) &&
                    (taps == 1 || (aligned16(state) && state_stride % 4 == 0));
   const int vthreads = channels / 4 >= 256 ? 256 : ((channels / 4 + 31) / 32) * 32;
   // the filter's blocks, and behind them one block per request (and chunk of channels) that leaves the new state
@@ -538,7 +542,7 @@ OI_API int oi_short_conv_strided(void* out, int out_dtype, long long out_stride,
   const dim3 vgrid(conv_blocks + ((update_state && taps > 1) ? requests : 0), vec ? (channels / 4 + vthreads - 1) / vthreads : 1);
 #define OI_CONV_VEC(TX, TO, KT)                                                                                          \
   oi_launch(short_conv_vec_kernel<TX, TO, KT>, vgrid, vthreads, 0, s, (TO*)out, (const TX*)x, w, w_dtype, state, state_stride, \
-            cu_seqlens, token_req, state_slots, state_phase, tokens, channels, taps, add_input, conv_blocks)
+            cu_seqlens, token_req, state_slots, state_phase, tokens, channels, taps, add_input, conv_blocks, x_stride, out_stride, act)
 #define OI_CONV_CASE(XD, OD, TX, TO)                                                                                     \
   if (x_dtype == XD && out_dtype == OD) {                                                                                \
     if (vec) {                                                                                                           \

@@ -187,6 +187,8 @@ OI_API int oi_attention_layer(const OiAttnStep* s, const OiAttnLayer* l, void* s
   const int tokens = s->tokens;
   if (tokens == 0) return OI_OK;
   const bool fused = l->rope_mode == 1 && s->tensor_core && s->fuse_rope && !l->interleaved;
+  OI_REQUIRE(!(fused && (l->mods.sinks || l->mods.slopes || l->mods.softcap > 0.f || l->mods.qt_every > 0)),
+             "attention_layer: a step with the rotation fused into the decode kernel cannot modify its scores");
   OI_REQUIRE(l->qkv && l->out && l->k_cache && l->v_cache && s->block_table && s->kv_lens && s->cu_seqlens,
              "attention_layer: a tensor of the step or of the layer is missing");
   OI_REQUIRE(l->rope_mode == 0 || ((!l->write_kv || s->slot_mapping) && (!l->cos_tab || s->positions)),
@@ -210,21 +212,22 @@ OI_API int oi_attention_layer(const OiAttnStep* s, const OiAttnLayer* l, void* s
                                     l->norm_dtype, l->eps, l->w_offset, l->cos_tab, l->sin_tab, l->rot_half, l->max_pos,
                                     s->positions, s->slot_mapping, l->write_kv, stream);
   }
-  if (s->num_tile_items && s->use_tcgen05)
+  const OiScoreMods* mods = (l->mods.sinks || l->mods.slopes || l->mods.softcap > 0.f || l->mods.qt_every > 0) ? &l->mods : nullptr;
+  if (s->num_tile_items && s->use_tcgen05 && !mods)
     OI_TRY(oi_attention_tcgen05(l->qkv, l->q_row_stride, tokens, l->out, l->out_row_stride, l->k_cache, l->v_cache,
                                 s->page_stride, s->page_size, s->num_pages, s->block_table, s->bt_stride, s->cu_seqlens,
                                 s->kv_lens, s->tile_items, s->num_tile_items, l->nq, l->nkv, l->hd, l->scale, l->window,
                                 s->row_splits, s->tile_split, s->part_o, s->part_lse, s->max_splits, stream));
   else if (s->num_tile_items)
-    OI_TRY(oi_attention_mma(l->qkv, l->q_row_stride, l->out, l->out_row_stride, l->k_cache, l->v_cache, s->page_stride,
-                            s->page_size, s->block_table, s->bt_stride, s->cu_seqlens, s->kv_lens, s->tile_items,
-                            s->num_tile_items, s->row_splits, tokens, s->tile_split, l->nq, l->nkv, l->hd, l->scale, l->window,
-                            s->part_o, s->part_lse, s->max_splits, s->rows_per_cta, stream));
+    OI_TRY(oi_attention_mma_mods(l->qkv, l->q_row_stride, l->out, l->out_row_stride, l->k_cache, l->v_cache, s->page_stride,
+                                 s->page_size, s->block_table, s->bt_stride, s->cu_seqlens, s->kv_lens, s->tile_items,
+                                 s->num_tile_items, s->row_splits, tokens, s->tile_split, l->nq, l->nkv, l->hd, l->scale, l->window,
+                                 s->part_o, s->part_lse, s->max_splits, s->rows_per_cta, mods, stream));
   if (s->num_decode_items)
-    OI_TRY(oi_attention_decode(l->qkv, l->q_row_stride, l->out, l->out_row_stride, l->k_cache, l->v_cache, s->page_stride,
-                               s->page_size, s->block_table, s->bt_stride, s->cu_seqlens, s->kv_lens, s->decode_items,
-                               s->num_decode_items, s->row_splits, tokens, l->nq, l->nkv, l->hd, l->scale, l->window,
-                               s->part_o, s->part_lse, s->max_splits, s->merge_in_kernel, stream));
+    OI_TRY(oi_attention_decode_mods(l->qkv, l->q_row_stride, l->out, l->out_row_stride, l->k_cache, l->v_cache, s->page_stride,
+                                    s->page_size, s->block_table, s->bt_stride, s->cu_seqlens, s->kv_lens, s->decode_items,
+                                    s->num_decode_items, s->row_splits, tokens, l->nq, l->nkv, l->hd, l->scale, l->window,
+                                    s->part_o, s->part_lse, s->max_splits, s->merge_in_kernel, mods, stream));
   return OI_OK;
 }
 

@@ -39,6 +39,35 @@ typedef struct OiScoreMods {
   int qt_every;          //   1 + qt_coef * ln(floor((p + 1) / qt_every) + 1), before the cap
 } OiScoreMods;
 
+#ifdef __CUDACC__
+constexpr float kLog2e = 1.4426950408889634f;
+
+// What a tensor-core attention kernel instantiated with MODS does to the raw dot products of one query row, leaving them in units of log2: the row's
+// temperature and the softmax scale, the cap (tanh through one exp2 and one division: 1 - 2 / (e^(2x) + 1), whose
+// absolute error stays near 1e-7 for every x), and the distance slope.
+struct RowMods {
+  float mul;      // no cap: scale * temperature * log2(e); with a cap: scale * temperature * 2 log2(e) / cap
+  float cap_l2;   // cap * log2(e), 0 without a cap
+  float slope_l2; // slope * log2(e)
+  __device__ __forceinline__ void init(const OiScoreMods& mods, float scale, int head, int pos) {
+    float sc = scale;
+    if (mods.qt_every > 0) sc *= 1.f + mods.qt_coef * logf((float)((pos + 1) / mods.qt_every) + 1.f);
+    cap_l2 = mods.softcap > 0.f ? mods.softcap * kLog2e : 0.f;
+    mul = mods.softcap > 0.f ? sc * (2.f * kLog2e) / mods.softcap : sc * kLog2e;
+    slope_l2 = mods.slopes ? mods.slopes[head] * kLog2e : 0.f;
+  }
+  __device__ __forceinline__ float apply(float s, int dist) const {
+    float x = s * mul;
+    if (cap_l2 > 0.f) {
+      float e;
+      asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(e) : "f"(x));
+      x = cap_l2 - __fdividef(2.f * cap_l2, e + 1.f);
+    }
+    return fmaf(-slope_l2, (float)dist, x);
+  }
+};
+#endif
+
 // argmax_noalloc.cu
 OI_API int oi_argmax_noalloc(int* out, const float* logits, int rows, int vocab, long long row_stride, void* stream);
 
@@ -54,6 +83,16 @@ OI_API int oi_attention_decode(const void* q, int q_row_stride, void* out, int o
        cu_seqlens, const int* kv_lens, const int* items, int num_items, const int* row_splits, int tokens, int nq, int
        nkv, int hd, float scale, int window, float* part_o, float* part_lse, int max_splits, int merge_in_kernel,
        void* stream);
+OI_API int oi_attention_decode_mods(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache,
+       const void* v_cache, long long page_stride, int page_size, const int* block_table, int bt_stride, const int*
+       cu_seqlens, const int* kv_lens, const int* items, int num_items, const int* row_splits, int tokens, int nq, int
+       nkv, int hd, float scale, int window, float* part_o, float* part_lse, int max_splits, int merge_in_kernel,
+       const OiScoreMods* mods, void* stream);
+OI_API int oi_attention_mma_mods(const void* q, int q_row_stride, void* out, int out_row_stride, const void* k_cache, const
+       void* v_cache, long long page_stride, int page_size, const int* block_table, int bt_stride, const int* cu_seqlens,
+       const int* kv_lens, const int* items, int num_items, const int* row_splits, int tokens, int any_split, int nq, int
+       nkv, int hd, float scale, int window, float* part_o, float* part_lse, int max_splits, int rows_per_cta,
+       const OiScoreMods* mods, void* stream);
 OI_API int oi_attention_decode_rope(const void* qkv, int q_row_stride, void* out, int out_row_stride, void* k_cache,
        void* v_cache, long long page_stride, int page_size, const int* block_table, int bt_stride, const int*
        cu_seqlens, const int* kv_lens, const int* items, int num_items, const int* row_splits, int tokens, int nq, int

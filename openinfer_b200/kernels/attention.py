@@ -340,7 +340,7 @@ def tcgen05_status() -> int:
 
 
 FUSE_ROPE_IN_DECODE = True
-MODS_ON_TENSOR_CORES = False   # layers that modify their scores run on the general kernel
+MODS_ON_TENSOR_CORES = True    # layers that modify their scores run on the mma.sync tile and decode kernels (False: the general kernel)
 
 
 def decode_takes_rope(qkv: torch.Tensor, ctx, group_step, nq: int, nkv: int, hd: int, window, cos, q_norm_w,
@@ -400,18 +400,19 @@ def attention_step(ctx, group_step, qkv: torch.Tensor, out: torch.Tensor, k_cach
         step.merge_in_kernel = 1 if plan.decode_merge_in_kernel else 0
         step.part_o = 0 if plan.part_o is None else plan.part_o.data_ptr()
         step.part_lse = 0 if plan.part_lse is None else plan.part_lse.data_ptr()
-        step.use_tcgen05 = 1 if (plan.num_tile_items and _tcgen05_takes(plan, qkv, out, k_cache, ctx.cache.page_size, nq, nkv,
+        # (the tcgen05 tile kernel and the rotation fused into the decode kernel take plain scores only)
+        step.use_tcgen05 = 1 if (not mods and plan.num_tile_items and _tcgen05_takes(plan, qkv, out, k_cache, ctx.cache.page_size, nq, nkv,
                                                                        hd, page_stride)) else 0
-        step.fuse_rope = 1 if decode_takes_rope(qkv, ctx, group_step, nq, nkv, hd, window, cos, q_norm_w, page_stride) else 0
+        step.fuse_rope = 1 if not mods and decode_takes_rope(qkv, ctx, group_step, nq, nkv, hd, window, cos, q_norm_w, page_stride) else 0
     ctx.scratch[key] = step
     return step
 
 
-def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nkv, hd, scale, window) -> bool:
+def attention_mma(q, out, k_cache, v_cache, page_stride, ctx, group_step, nq, nkv, hd, scale, window, mods=None) -> bool:
     """The tensor-core kernels alone, when they cover the shape (bfloat16, head_dim 32, 64 or 128): q is ready and the
-    cache is written. Returns whether they ran."""
-    step = attention_step(ctx, group_step, q, out, k_cache, page_stride, nq, nkv, hd, window)
+    cache is written. ``mods``: a ``native.ScoreMods`` when the scores are modified. Returns whether they ran."""
+    step = attention_step(ctx, group_step, q, out, k_cache, page_stride, nq, nkv, hd, window, mods=mods is not None)
     if not step.tensor_core:
         return False
-    run_attention(step, attention_layer(q, out, k_cache, v_cache, nq, nkv, hd, scale, window, write_kv=False, rope_mode=0))
+    run_attention(step, attention_layer(q, out, k_cache, v_cache, nq, nkv, hd, scale, window, write_kv=False, rope_mode=0, mods=mods))
     return True

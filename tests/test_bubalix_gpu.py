@@ -126,7 +126,7 @@ def test_latent_norm_rotation_and_store_kernel(dtype, heads, rank, rot, page):
     proj = (torch.randn(tokens, width, generator=g) * 2).to(dtype)
     w = (1 + 0.1 * torch.randn(rank, generator=g)).to(torch.bfloat16)
     positions = [0, 1, 77, 300, 5, 511, 64]
-    slots = [3, 0, 17, page * pages_total - 1, -1, 8, 1]
+    slots = [3, 0, 6, page * pages_total - 1, -1, 8, 1]
     store = torch.full((pages_total, page, 1, row), 5.0, dtype=dtype, device="cuda")
     pd = _dev(proj.clone())
     ops.latent_rope_store(store, page * row, pd, lat_off, rank, _dev(w), 1e-5, 0.0, cos, sin, _i32(positions), _i32(slots), heads, row, rank)
@@ -292,24 +292,26 @@ def test_mechanisms_show_in_the_logits(tmp_path):
         wrong = plain.forward(c, t, toks)
         return min((got[:50] - wrong[:50]).abs().max().item(), (got[50:] - wrong[50:]).abs().max().item()) / size
 
+    # every change below moves the plain logits by 4e-4 of their size or more; the engine is within 1e-4 (in fact far closer)
+    seen = max(2e-4, 20 * (got - ref).abs().max().item() / size)
     L0, L1 = (lambda c: c["layers"][0]["mixer"]), (lambda c: c["layers"][1]["mixer"])
-    assert without(lambda c: L0(c).pop("softcap")) > 1e-2
-    assert without(lambda c: L0(c).pop("q_temp")) > 1e-2
-    assert without(lambda c: L0(c)["q_temp"].__setitem__("every", 10)) > 1e-3            # floor((p + 1) / every): off by one
-    assert without(lambda c: L0(c).pop("conv")) > 1e-2
-    assert without(lambda c: L0(c)["mask"].__setitem__("size", 17)) > 1e-3
-    assert without(lambda c: L0(c)["mask"].__setitem__("size", 19)) > 1e-3
-    assert without(lambda c: L1(c)["rot"].pop("scaling")) > 1e-3
-    assert without(lambda c: L1(c)["rot"].__setitem__("base", 200.0)) > 1e-3
-    assert without(None, lambda t: t.__setitem__("l0.mix.sink", t["l0.mix.sink"] - 40.0)) > 1e-2
-    assert without(None, lambda t: t.__setitem__("l1.mix.sink", t["l1.mix.sink"] - 40.0)) > 1e-2
-    assert without(None, lambda t: t.__setitem__("l0.mix.g", t["l0.mix.g"] * 0.0)) > 1e-2
-    assert without(None, lambda t: t.__setitem__("l1.mix.g", t["l1.mix.g"] * 0.0)) > 1e-2
-    assert without(None, lambda t: t.__setitem__("l0.mlp.table", (t["l0.mlp.table"] + 1) % 5)) > 1e-2
-    assert without(lambda c: c["layers"][0]["mlp"].pop("shared")) > 1e-2
-    assert without(lambda c: c.pop("token_side")) > 1e-2
-    assert without(lambda c: c.pop("embedding")) > 1e-2
-    assert without(lambda c: c["norm"].__setitem__("eps", 1e-1)) > 1e-3
+    assert without(lambda c: L0(c).pop("softcap")) > seen
+    assert without(lambda c: L0(c).pop("q_temp")) > seen
+    assert without(lambda c: L0(c)["q_temp"].__setitem__("every", 10)) > seen            # floor((p + 1) / every): off by one
+    assert without(lambda c: L0(c).pop("conv")) > seen
+    assert without(lambda c: L0(c)["mask"].__setitem__("size", 17)) > seen
+    assert without(lambda c: L0(c)["mask"].__setitem__("size", 19)) > seen
+    assert without(lambda c: L1(c)["rot"].pop("scaling")) > seen
+    assert without(lambda c: L1(c)["rot"].__setitem__("base", 200.0)) > seen
+    assert without(None, lambda t: t.__setitem__("l0.mix.sink", t["l0.mix.sink"] - 40.0)) > seen
+    assert without(None, lambda t: t.__setitem__("l1.mix.sink", t["l1.mix.sink"] - 40.0)) > seen
+    assert without(None, lambda t: t.__setitem__("l0.mix.g", t["l0.mix.g"] * 0.0)) > seen
+    assert without(None, lambda t: t.__setitem__("l1.mix.g", t["l1.mix.g"] * 0.0)) > seen
+    assert without(None, lambda t: t.__setitem__("l0.mlp.table", (t["l0.mlp.table"] + 1) % 5)) > seen
+    assert without(lambda c: c["layers"][0]["mlp"].pop("shared")) > seen
+    assert without(lambda c: c.pop("token_side")) > seen
+    assert without(lambda c: c.pop("embedding")) > seen
+    assert without(lambda c: c["norm"].__setitem__("eps", 1e-1)) > seen
 
 
 # ---------------------------------------------------------------------------------------------- the model
@@ -378,24 +380,35 @@ def test_a_slot_used_again_starts_from_zero(folders):
         check_trace(runner, folders[name], {"r": toks}, trace_tail({"r": toks}, tail=10), "float32", f"slot/{seed}")
 
 
-def test_window_edges_show_in_the_logits(folders):
-    """The comparison is sharp enough to see a window that is one key off: the plain implementation with every window
-    one longer or one shorter differs from the engine by far more than the bound, at prompt rows and at decoded ones."""
-    name = "A"
-    cfg, tensors = read_folder(folders[name])
+def test_window_edges_show_in_the_logits(tmp_path):
+    """The comparison is sharp enough to see a window that is one key off: the plain implementation with a window one
+    longer or one shorter differs from the engine by far more than the engine does from the right one, at prompt rows and
+    at decoded ones. The model is made for it: sharp softmaxes, sinks far down, and in the layer with the long window few
+    heads, so that the slope of the last one leaves the window's oldest key its weight."""
+    from safetensors.torch import save_file
+    cfg = model(120, 48, [
+        attn(4, 2, 16, 24, 1.1, window=21, conv=3, q_temp=(0.4, 32), softcap=12.0, mlp=moe(16, 7, 1, shared=32)),
+        attn(3, 1, 24, 40, 1.6, window=70, conv=2, softcap=8.0, mlp=None),
+    ], eps=1e-5, scale=0.7, side=6)
+    path = make_folder(str(tmp_path / "edges"), cfg, 77)
+    raw, tensors = read_folder(path)
+    tensors = dict(tensors)
+    for layer in (0, 1):
+        tensors[f"l{layer}.mix.sink"] = tensors[f"l{layer}.mix.sink"] - 20.0
+    save_file({k: v.contiguous() for k, v in tensors.items()}, path + "/model.safetensors")
     toks = tokens_for(cfg, 150, 9)
-    runner = runner_for(folders[name], "float32")
+    runner = runner_for(path, "float32", max_tokens=256)
     got = replay_in_process(runner, trace_tail({"e": toks}, tail=60))["e"].double()
-    ref = oracle(folders[name], toks)
-    compare(got, folders[name], toks, "float32", "edges")
+    ref = plain.forward(raw, tensors, toks)
     scale = ref.pow(2).mean().sqrt().item()
-    for layer in (1, 2):
+    assert (got - ref).abs().max().item() < 2e-5 * scale
+    for layer in (0, 1):
         for d in (-1, 1):
-            off = json.loads(json.dumps(cfg))
+            off = json.loads(json.dumps(raw))
             off["layers"][layer]["mixer"]["mask"]["size"] += d
             wrong = plain.forward(off, tensors, toks)
-            assert (got[75:90] - wrong[75:90]).abs().max().item() > 1e-3 * scale, "a window one key off would not be noticed in a prompt"
-            assert (got[90:] - wrong[90:]).abs().max().item() > 1e-3 * scale, "a window one key off would not be noticed while decoding"
+            assert (got[75:90] - wrong[75:90]).abs().max().item() > 3e-4 * scale, "a window one key off would not be noticed in a prompt"
+            assert (got[90:] - wrong[90:]).abs().max().item() > 3e-4 * scale, "a window one key off would not be noticed while decoding"
             assert (ref[:20] - wrong[:20]).abs().max().item() < 1e-9             # before any window is full the two agree
 
 

@@ -81,6 +81,39 @@ def test_short_conv_kernel_portions_and_state(taps, channels, out_dtype):
         assert (state[1] == 7.0).all()                             # a slot no request of the steps held
 
 
+@pytest.mark.parametrize("taps,channels,act", [(4, 64, "none"), (3, 1032, "silu"), (2, 40, "silu"), (5, 30, "none"), (9, 32, "silu")])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_short_conv_on_columns_of_wider_rows(taps, channels, act, dtype):
+    """The filter alone (no input added) on a slice of columns of a wider buffer, into a slice of another, with and without
+    the activation, in two steps of unequal portions: the columns beside the slices stay as they were."""
+    from openinfer_b200.kernels import ops
+    g = torch.Generator().manual_seed(taps + channels)
+    lens, cuts, slots = [9, 2 * taps + 20], [[2, 7], [taps + 17, taps + 3]], [1, 0]
+    seqs = [torch.randn(n, channels, generator=g).to(dtype) for n in lens]
+    w = torch.randn(channels, taps, generator=g).to(torch.bfloat16)
+    want = [plain.causal_conv(s.double(), w.double()) for s in seqs]
+    if act == "silu":
+        want = [v * torch.sigmoid(v) for v in want]
+    state = torch.zeros((2, 2, taps - 1, channels), device="cuda")
+    at = [0, 0]
+    for step in range(2):
+        rows = [seqs[b][at[b]: at[b] + cuts[b][step]] for b in range(2)]
+        n = sum(r.shape[0] for r in rows)
+        wide_in = torch.full((n, channels + 24), 3.0, dtype=dtype, device="cuda")
+        wide_in[:, 16: 16 + channels] = _dev(torch.cat(rows))
+        wide_out = torch.full((n, channels + 12), 5.0, dtype=dtype, device="cuda")
+        cu = torch.tensor([0, rows[0].shape[0], n], dtype=torch.int32, device="cuda")
+        req = torch.cat([torch.full((r.shape[0],), b, dtype=torch.int32) for b, r in enumerate(rows)]).cuda()
+        phase = torch.full((2,), step & 1, dtype=torch.int32, device="cuda")
+        ops.short_conv_act(wide_out[:, 8: 8 + channels], wide_in[:, 16: 16 + channels], _dev(w), state, cu, req,
+                           torch.tensor(slots, dtype=torch.int32, device="cuda"), phase, act=act, add_input=False)
+        ref = torch.cat([want[b][at[b]: at[b] + cuts[b][step]] for b in range(2)])
+        tol = 1e-5 if dtype == torch.float32 else 1e-2
+        assert (wide_out[:, 8: 8 + channels].double().cpu() - ref).abs().max().item() <= tol * max(1.0, ref.abs().max().item())
+        assert (wide_out[:, :8] == 5.0).all() and (wide_out[:, 8 + channels:] == 5.0).all() and (wide_in[:, :16] == 3.0).all()
+        at = [a + c[step] for a, c in zip(at, cuts)]
+
+
 @pytest.mark.parametrize("a_dtype", [torch.float32, torch.bfloat16])
 def test_branch_norm_add_and_history_kernels(a_dtype):
     from openinfer_b200.kernels import ops

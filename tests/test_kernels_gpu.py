@@ -401,7 +401,8 @@ def _pages_in_runs(total_pages, seed):
     return [p for run in runs for p in run]
 
 
-def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None, page_runs=False):
+def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None, page_runs=False, mods=None):
+    """``mods``: (cap, temperature (coef, every) or None, slopes?, sinks?) for scores as a layer may modify them."""
     from openinfer_b200.kernels import attention as A
     torch.manual_seed(seed)
     dtype = torch.bfloat16
@@ -442,8 +443,20 @@ def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None
         A.plan_items = forced
     try:
         out = torch.full((T, nq * hd), float("nan"), device=DEV, dtype=dtype)
+        scale = (2.5 if mods else 1.0) / math.sqrt(hd)          # modified scores: sharp enough to reach the cap
+        score_mods = None
+        if mods:
+            from openinfer_b200.kernels import native
+            import plain_bubalix
+            cap, temperature, with_slopes, with_sinks = mods
+            sinks = torch.randn(nq) + 1.0
+            slopes = plain_bubalix.distance_slopes(nq, torch.float32)
+            sinks_d, slopes_d = sinks.to(DEV), slopes.to(DEV)
+            score_mods = native.ScoreMods(sinks=sinks_d.data_ptr() if with_sinks else None, slopes=slopes_d.data_ptr() if with_slopes else None,
+                                          softcap=float(cap or 0.0), qt_coef=temperature[0] if temperature else 0.0,
+                                          qt_every=temperature[1] if temperature else 0)
         ran = A.attention_mma(wide[:, : nq * hd], out, cache[:, 1, 0], cache[:, 1, 1], cache.stride(0), ctx, grp,
-                              nq, nkv, hd, 1.0 / math.sqrt(hd), window)
+                              nq, nkv, hd, scale, window, mods=score_mods)
     finally:
         if force_splits:
             A.plan_items = old
@@ -452,14 +465,19 @@ def _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, seed=0, force_splits=None
     plan = next(iter(ctx.scratch.values()))
     step = [v for k, v in ctx.scratch.items() if k[0] == "attention_step"][0]
     if (A.USE_TCGEN05 and hd == 128 and plan.rows_per_cta == 128 and 128 % (nq // nkv) == 0 and P >= 16 and P & (P - 1) == 0
-            and plan.num_tile_items):
+            and plan.num_tile_items and not mods):
         assert step.use_tcgen05, "the tcgen05 kernel covers this shape and did not run"
-    scale = 1.0 / math.sqrt(hd)
     row = 0
     for b, (n, kv) in enumerate(zip(q_lens, kv_lens)):
         qq = torch.zeros(kv, nq, hd)
         qq[kv - n:] = q[row: row + n].float()
-        ref = plain.causal_attention(qq, ks[b], vs[b], scale, window)[kv - n:]
+        if mods:
+            ref = plain_bubalix.scored_attention(
+                qq.double(), ks[b].double(), vs[b].double(), scale, window,
+                sinks.double() if with_sinks else torch.full((nq,), -math.inf, dtype=torch.float64), cap, slopes.double() if with_slopes else None,
+                plain_bubalix.query_temperature(kv, temperature[0], temperature[1], torch.float64) if temperature else None)[kv - n:].float()
+        else:
+            ref = plain.causal_attention(qq, ks[b], vs[b], scale, window)[kv - n:]
         got = out[row: row + n].float().cpu().view(n, nq, hd)
         assert torch.isfinite(got).all(), f"request {b}: unwritten or non-finite output"
         err = (got - ref).abs()
@@ -485,6 +503,20 @@ def test_attention_mma_mixed_batch(nq, nkv, hd, P, window, tcgen05, monkeypatch)
     # short portions only: the small tile
     plan = _mma_case(nq, nkv, hd, P, window, [3, 1, 2], [70, 131, 300])
     assert plan.rows_per_cta == (64 if 3 * (nq // nkv) < 128 else 128)
+
+
+@pytest.mark.parametrize("mods", [(6.0, (0.6, 16), True, True), (None, None, False, True), (3.0, None, True, False), (None, (1.5, 50), False, False)])
+@pytest.mark.parametrize("nq,nkv,hd,P,window", [(32, 8, 128, 16, None), (6, 2, 32, 16, 100), (8, 1, 64, 8, 17), (16, 1, 128, 16, None), (4, 4, 64, 32, 70)])
+def test_attention_mma_with_modified_scores(nq, nkv, hd, P, window, mods):
+    """Sink, distance slopes, cap and query temperature inside the tile and decode kernels: prompt portions beside single
+    tokens; decode rows cut into slices that clusters merge, that the second kernel merges, and through the tile kernel in
+    slices (the sink counts once, in the slice of the row's first keys)."""
+    q_lens = [9, 1, 70, 1, 33, 2]
+    kv_lens = [70, 131, 70, 1, 300, 65]
+    _mma_case(nq, nkv, hd, P, window, q_lens, kv_lens, mods=mods)
+    long = [1, 63, 64, 65, 129, 700, 1025]
+    for force in (None, "max", "none", "tiles", "tiles_whole"):
+        _mma_case(nq, nkv, hd, P, window, [1] * len(long), long, force_splits=force, mods=mods)
 
 
 @pytest.mark.parametrize("nq,nkv,hd", [(32, 8, 128), (6, 2, 32), (8, 1, 64)])
