@@ -113,11 +113,11 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
   }
 }
 
-// One block per expert e. sorted[first_e + i] = the i-th pair (in ascending pair number) that chose e; tiles of kTileM
+// One block per expert e. sorted[first_e + i] = the i-th pair (in ascending pair number) that chose e; tiles of tile_m
 // sorted places that belong to one expert: tile_info[3 * t] = expert, first place, rows. tile_info's last word
 // (at 3 * max_tiles) is the number of tiles.
 __global__ void moe_group_kernel(const int* __restrict__ ids, int pairs, int E, int* __restrict__ sorted, int* __restrict__ tile_info,
-                                 int max_tiles) {
+                                 int max_tiles, int tile_m) {
   pdl_start();
   extern __shared__ int hist[];       // [E] counts, then [warps] scan scratch
   __shared__ int s_first, s_tile0, s_count;
@@ -132,7 +132,7 @@ __global__ void moe_group_kernel(const int* __restrict__ ids, int pairs, int E, 
   if (threadIdx.x == 0) {
     int first = 0, tile0 = 0, total = 0;
     for (int i = 0; i < E; ++i) {
-      const int tiles = (hist[i] + kTileM - 1) / kTileM;
+      const int tiles = (hist[i] + tile_m - 1) / tile_m;
       if (i < e) {
         first += hist[i];
         tile0 += tiles;
@@ -144,11 +144,11 @@ __global__ void moe_group_kernel(const int* __restrict__ ids, int pairs, int E, 
   }
   __syncthreads();
   const int first = s_first, tile0 = s_tile0, count = s_count;
-  for (int t = threadIdx.x; t * kTileM < count; t += blockDim.x) {
+  for (int t = threadIdx.x; t * tile_m < count; t += blockDim.x) {
     if (tile0 + t < max_tiles) {
       tile_info[3 * (tile0 + t)] = e;
-      tile_info[3 * (tile0 + t) + 1] = first + t * kTileM;
-      tile_info[3 * (tile0 + t) + 2] = count - t * kTileM < kTileM ? count - t * kTileM : kTileM;
+      tile_info[3 * (tile0 + t) + 1] = first + t * tile_m;
+      tile_info[3 * (tile0 + t) + 2] = count - t * tile_m < tile_m ? count - t * tile_m : tile_m;
     }
   }
   // stable compaction of the pairs that chose e
@@ -184,7 +184,10 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ A, 
   pdl_wait();    // no early trigger: waiting blocks of the next kernel would share the SMs with this product
   const int tile = blockIdx.x;
   if (tile >= tile_info[3 * max_tiles]) return;
-  const int e = tile_info[3 * tile], place0 = tile_info[3 * tile + 1], m_rows = tile_info[3 * tile + 2];
+  // a block takes kTileM rows: of a longer tile, the part that blockIdx.z names
+  const int e = tile_info[3 * tile], place0 = tile_info[3 * tile + 1] + (int)blockIdx.z * kTileM;
+  const int m_rows = min(tile_info[3 * tile + 2] - (int)blockIdx.z * kTileM, kTileM);
+  if (m_rows <= 0) return;
   const int n0 = blockIdx.y * kTileN;
   __shared__ float As[kTileK][kTileM + 1];
   __shared__ float Wg[kTileK][kTileN + 1];
@@ -298,7 +301,10 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const bf16* __restric
   pdl_wait();
   const int tile = blockIdx.x;
   if (tile >= tile_info[3 * max_tiles]) return;
-  const int e = tile_info[3 * tile], place0 = tile_info[3 * tile + 1], m_rows = tile_info[3 * tile + 2];
+  // a block takes kTileM rows: of a longer tile, the part that blockIdx.z names
+  const int e = tile_info[3 * tile], place0 = tile_info[3 * tile + 1] + (int)blockIdx.z * kTileM;
+  const int m_rows = min(tile_info[3 * tile + 2] - (int)blockIdx.z * kTileM, kTileM);
+  if (m_rows <= 0) return;
   const int n0 = blockIdx.y * kTileN;
   constexpr int kPad = kTileK + 8;
   __shared__ __align__(16) bf16 As[kTileM][kPad];
@@ -370,6 +376,119 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_kernel(const bf16* __restric
     }
 }
 
+// The same products for steps whose experts have many rows each: tiles of kBigM sorted places (see oi_moe_tile_rows), so
+// that an expert's weights are read from the second-level cache once per 128 rows and not once per 32. 8 warps, warp w
+// the 32 rows (w & 3) x the 32 columns (w >> 2) of the 128 x 64 tile (and the same columns of the up rows); operand tiles
+// of 32 k arrive by cp.async in two buffers, so that a tile's copies run beside the products of the one before. A row's
+// sums are formed in the same order as in the kernel above.
+constexpr int kBigM = 128;
+
+__device__ __forceinline__ void moe_cp16(void* dst, const void* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int n = valid ? 16 : 0;          // 0: the 16 bytes are filled with zeros and src is not read
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n));
+}
+
+template <typename TO, bool kGlu>
+__global__ void __launch_bounds__(256) moe_gemm_mma_big_kernel(const bf16* __restrict__ A, long long lda, int a_div, const bf16* __restrict__ Wt,
+                                                               long long w_expert_stride, TO* __restrict__ out, long long ld_out,
+                                                               int scatter, const int* __restrict__ sorted,
+                                                               const int* __restrict__ tile_info, int max_tiles, int N, int K, float limit,
+                                                               int act) {
+  pdl_wait();
+  const int tile = blockIdx.x;
+  if (tile >= tile_info[3 * max_tiles]) return;
+  const int e = tile_info[3 * tile], place0 = tile_info[3 * tile + 1], m_rows = min(tile_info[3 * tile + 2], kBigM);
+  const int n0 = blockIdx.y * kTileN;
+  constexpr int kPad = kTileK + 8;
+  __shared__ __align__(16) bf16 As[2][kBigM][kPad];
+  __shared__ __align__(16) bf16 Bg[2][kTileN][kPad];
+  __shared__ __align__(16) bf16 Bu[2][kGlu ? kTileN : 1][kPad];
+  __shared__ int src[kBigM];
+  if (threadIdx.x < kBigM) {
+    int r = -1;
+    if ((int)threadIdx.x < m_rows) {
+      const int place = place0 + threadIdx.x;
+      r = a_div > 0 ? sorted[place] / a_div : place;
+    }
+    src[threadIdx.x] = r;
+  }
+  __syncthreads();
+  const bf16* We = Wt + (size_t)e * w_expert_stride;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, tg = lane & 3;
+  const int wm = (warp & 3) * 32, wn = (warp >> 2) * 32;
+  // this thread's 16-byte pieces of a stage: two of A (rows m, m + 64), one of the gate rows and one of the up rows
+  const int lm = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 8;
+  const int r0 = src[lm], r1 = src[lm + 64];
+  const bool n_ok = n0 + lm < N;
+  auto load = [&](int k0, int buf) {
+    const bool k_ok = k0 + lk < K;
+    moe_cp16(&As[buf][lm][lk], (r0 >= 0 && k_ok) ? A + (size_t)r0 * lda + k0 + lk : A, r0 >= 0 && k_ok);
+    moe_cp16(&As[buf][lm + 64][lk], (r1 >= 0 && k_ok) ? A + (size_t)r1 * lda + k0 + lk : A, r1 >= 0 && k_ok);
+    const bool ok = n_ok && k_ok;
+    moe_cp16(&Bg[buf][lm][lk], ok ? We + (size_t)(n0 + lm) * K + k0 + lk : We, ok);
+    if (kGlu) moe_cp16(&Bu[buf][lm][lk], ok ? We + (size_t)(N + n0 + lm) * K + k0 + lk : We, ok);
+    asm volatile("cp.async.commit_group;\n" ::);
+  };
+  float acc[2][4][4] = {}, accu[kGlu ? 2 : 1][4][4] = {};
+  load(0, 0);
+  int buf = 0;
+  for (int k0 = 0; k0 < K; k0 += kTileK, buf ^= 1) {
+    if (k0 + kTileK < K) {
+      load(k0 + kTileK, buf ^ 1);
+      asm volatile("cp.async.wait_group 1;\n" ::);
+    } else {
+      asm volatile("cp.async.wait_group 0;\n" ::);
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < kTileK; kk += 16) {
+      unsigned a[2][4];
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        a[i][0] = *reinterpret_cast<const unsigned*>(&As[buf][wm + 16 * i + g][kk + 2 * tg]);
+        a[i][1] = *reinterpret_cast<const unsigned*>(&As[buf][wm + 16 * i + g + 8][kk + 2 * tg]);
+        a[i][2] = *reinterpret_cast<const unsigned*>(&As[buf][wm + 16 * i + g][kk + 2 * tg + 8]);
+        a[i][3] = *reinterpret_cast<const unsigned*>(&As[buf][wm + 16 * i + g + 8][kk + 2 * tg + 8]);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        unsigned b[2];
+        b[0] = *reinterpret_cast<const unsigned*>(&Bg[buf][wn + 8 * j + g][kk + 2 * tg]);
+        b[1] = *reinterpret_cast<const unsigned*>(&Bg[buf][wn + 8 * j + g][kk + 2 * tg + 8]);
+        mma_bf16_16816(acc[0][j], a[0], b);
+        mma_bf16_16816(acc[1][j], a[1], b);
+        if (kGlu) {
+          b[0] = *reinterpret_cast<const unsigned*>(&Bu[buf][wn + 8 * j + g][kk + 2 * tg]);
+          b[1] = *reinterpret_cast<const unsigned*>(&Bu[buf][wn + 8 * j + g][kk + 2 * tg + 8]);
+          mma_bf16_16816(accu[0][j], a[0], b);
+          mma_bf16_16816(accu[kGlu ? 1 : 0][j], a[1], b);
+        }
+      }
+    }
+    __syncthreads();       // the buffer is free for the copies of the stage after the next
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int m = wm + 16 * i + g + 8 * h;
+      if (m >= m_rows) continue;
+      const int place = place0 + m;
+      const size_t row = scatter ? (size_t)sorted[place] : (size_t)place;
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int n = n0 + wn + 8 * j + 2 * tg + c;
+          if (n >= N) continue;
+          float v = acc[i][j][2 * h + c];
+          if (kGlu) v = glu_act<false>(v, accu[kGlu ? i : 0][j][2 * h + c], act, limit);
+          out[row * ld_out + n] = from_f32<TO>(v);
+        }
+    }
+}
+
 // The same two products for steps of few rows (at most two pairs an expert on average): one block per (pair, 16 output
 // rows), a warp per output row at a time, the pair's input row in shared memory as float32, the expert's rows read 16 bytes
 // at a time. No grouping is needed: pair p reads row p / a_div (a_div 0: row p) and writes row p.
@@ -435,6 +554,10 @@ __global__ void moe_combine_kernel(float* __restrict__ out, const float* __restr
 
 OI_API int oi_moe_max_tiles(int pairs, int experts) { return pairs / kTileM + experts; }
 
+// Sorted places per tile: 128 where the experts have 64 rows and more on average (the weights are then read once per 128
+// rows), otherwise 32 (fewer rows that are computed for nothing). A function of the step's size alone.
+OI_API int oi_moe_tile_rows(int pairs, int experts) { return (long long)pairs >= 64LL * experts ? kBigM : kTileM; }
+
 // Steps of at most this many (row, choice) pairs take the row-by-row products and need no grouping.
 OI_API int oi_moe_small(int pairs, int experts) { return pairs <= 2 * experts && pairs <= 64; }
 
@@ -457,7 +580,7 @@ OI_API int oi_moe_route(const void* x, int dtype, long long ldx, const void* w_r
   OI_CHECK_LAUNCH();
   const int pairs = rows * top;
   if (oi_moe_small(pairs, E)) return OI_OK;      // few rows: the products go pair by pair and need no grouping
-  oi_launch(moe_group_kernel, E, 256, (size_t)(E + 8) * sizeof(int), s, (const int*)ids, pairs, E, sorted, tile_info, oi_moe_max_tiles(pairs, E));
+  oi_launch(moe_group_kernel, E, 256, (size_t)(E + 8) * sizeof(int), s, (const int*)ids, pairs, E, sorted, tile_info, oi_moe_max_tiles(pairs, E), oi_moe_tile_rows(pairs, E));
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
@@ -490,7 +613,7 @@ OI_API int oi_moe_route_table(const int* token_ids, const int* table, int rows, 
   oi_launch(moe_table_kernel, (pairs + 127) / 128, 128, 0, s, token_ids, table, rows, vocab, E, top, 1.f / (float)top, ids, wts);
   OI_CHECK_LAUNCH();
   if (oi_moe_small(pairs, E)) return OI_OK;
-  oi_launch(moe_group_kernel, E, 256, (size_t)(E + 8) * sizeof(int), s, (const int*)ids, pairs, E, sorted, tile_info, oi_moe_max_tiles(pairs, E));
+  oi_launch(moe_group_kernel, E, 256, (size_t)(E + 8) * sizeof(int), s, (const int*)ids, pairs, E, sorted, tile_info, oi_moe_max_tiles(pairs, E), oi_moe_tile_rows(pairs, E));
   OI_CHECK_LAUNCH();
   return OI_OK;
 }
@@ -529,7 +652,10 @@ OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w
     OI_CHECK_LAUNCH();
     return OI_OK;
   }
-  const dim3 g1(max_tiles, (F + kTileN - 1) / kTileN), g2(max_tiles, (W + kTileN - 1) / kTileN);
+  const int tile_rows = oi_moe_tile_rows(pairs, E), subs = tile_rows / kTileM;
+  const bool big = tile_rows == kBigM;
+  const dim3 g1(max_tiles, (F + kTileN - 1) / kTileN, subs), g2(max_tiles, (W + kTileN - 1) / kTileN, subs);
+  const dim3 b1(max_tiles, (F + kTileN - 1) / kTileN), b2(max_tiles, (W + kTileN - 1) / kTileN);
   if (dtype == OI_F32) {
     oi_launch(moe_gemm_kernel<float, float, true>, g1, 256, 0, s, (const float*)x, ldx, top, (const float*)w_gate_up, (long long)2 * F * W,
               (float*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit, glu);
@@ -540,14 +666,20 @@ OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w
     // tensor cores when every row of the operands starts on a 16-byte boundary
     const bool tc1 = W % 8 == 0 && ldx % 8 == 0 && (uintptr_t)x % 16 == 0 && (uintptr_t)w_gate_up % 16 == 0;
     const bool tc2 = F % 8 == 0 && (uintptr_t)act % 16 == 0 && (uintptr_t)w_down % 16 == 0;
-    if (tc1)
+    if (tc1 && big)
+      oi_launch(moe_gemm_mma_big_kernel<bf16, true>, b1, 256, 0, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up, (long long)2 * F * W,
+                (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit, glu);
+    else if (tc1)
       oi_launch(moe_gemm_mma_kernel<bf16, true>, g1, 256, 0, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up, (long long)2 * F * W,
                 (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit, glu);
     else
       oi_launch(moe_gemm_kernel<bf16, bf16, true>, g1, 256, 0, s, (const bf16*)x, ldx, top, (const bf16*)w_gate_up, (long long)2 * F * W,
                 (bf16*)act, (long long)F, 0, sorted, tile_info, max_tiles, F, W, limit, glu);
     OI_CHECK_LAUNCH();
-    if (tc2)
+    if (tc2 && big)
+      oi_launch(moe_gemm_mma_big_kernel<float, false>, b2, 256, 0, s, (const bf16*)act, (long long)F, 0, (const bf16*)w_down, (long long)W * F,
+                y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f, 0);
+    else if (tc2)
       oi_launch(moe_gemm_mma_kernel<float, false>, g2, 256, 0, s, (const bf16*)act, (long long)F, 0, (const bf16*)w_down, (long long)W * F,
                 y, (long long)W, 1, sorted, tile_info, max_tiles, W, F, 0.f, 0);
     else

@@ -157,6 +157,7 @@ OI_API int oi_scaled_sum(float* out, const float* a, const float* b, float ca, f
 // moe.cu: routed experts
 OI_API int oi_moe_max_tiles(int pairs, int experts);
 OI_API int oi_moe_small(int pairs, int experts);
+OI_API int oi_moe_tile_rows(int pairs, int experts);
 OI_API int oi_moe_route(const void* x, int dtype, long long ldx, const void* w_router, int w_dtype, int rows, int K, int
        E, int top, int* ids, float* wts, int* sorted, int* tile_info, void* stream);
 OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w_gate_up, const void* w_down, int rows,

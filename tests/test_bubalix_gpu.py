@@ -188,10 +188,13 @@ def test_sum_of_sublayers_token_gate_and_table_routing_kernels():
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rows,W,F,E,top,shared", [(1, 40, 24, 5, 2, 16), (37, 64, 16, 3, 1, 0), (200, 96, 40, 16, 4, 24), (9, 36, 70, 40, 3, 10),
-                                                   (64, 128, 96, 4, 4, 0), (300, 64, 32, 12, 1, 48)])
+                                                   (64, 128, 96, 4, 4, 0), (300, 64, 32, 12, 1, 48),
+                                                   (700, 72, 40, 3, 2, 16), (150, 64, 200, 2, 1, 0), (1100, 256, 136, 5, 3, 0)])
 def test_experts_by_table_kernels(dtype, rows, W, F, E, top, shared):
     """Experts chosen by the token id through a table, each weighted 1 / top, plus an expert every row uses, against the
-    plain statement row by row; a row's result does not depend on the rows beside it."""
+    plain statement row by row; a row's result does not depend on the rows beside it (steps whose experts have 64 rows and
+    more on average take tiles of 128 rows, smaller ones tiles of 32, the smallest go pair by pair: the last three cases
+    compare a row across them)."""
     from openinfer_b200.kernels import ops
     g = torch.Generator().manual_seed(rows + E)
     vocab = 61
