@@ -389,6 +389,11 @@ __device__ __forceinline__ void moe_cp16(void* dst, const void* src, bool valid)
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(d), "l"(src), "r"(n));
 }
 
+__device__ __forceinline__ void ldsm4(unsigned (&r)[4], const void* row) {
+  const unsigned addr = (unsigned)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr) : "memory");
+}
+
 template <typename TO, bool kGlu>
 __global__ void __launch_bounds__(256) moe_gemm_mma_big_kernel(const bf16* __restrict__ A, long long lda, int a_div, const bf16* __restrict__ Wt,
                                                                long long w_expert_stride, TO* __restrict__ out, long long ld_out,
@@ -443,26 +448,26 @@ __global__ void __launch_bounds__(256) moe_gemm_mma_big_kernel(const bf16* __res
     __syncthreads();
 #pragma unroll
     for (int kk = 0; kk < kTileK; kk += 16) {
+      // ldmatrix: lanes 8 q .. 8 q + 7 name the rows of the q-th 8 x 8 piece. A: pieces (rows 0-7, k 0-7), (rows 8-15,
+      // k 0-7), (rows 0-7, k 8-15), (rows 8-15, k 8-15); weights: (columns 0-7, k 0-7), (0-7, k 8-15), (8-15, k 0-7), (8-15, k 8-15)
       unsigned a[2][4];
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        a[i][0] = *reinterpret_cast<const unsigned*>(&As[buf][wm + 16 * i + g][kk + 2 * tg]);
-        a[i][1] = *reinterpret_cast<const unsigned*>(&As[buf][wm + 16 * i + g + 8][kk + 2 * tg]);
-        a[i][2] = *reinterpret_cast<const unsigned*>(&As[buf][wm + 16 * i + g][kk + 2 * tg + 8]);
-        a[i][3] = *reinterpret_cast<const unsigned*>(&As[buf][wm + 16 * i + g + 8][kk + 2 * tg + 8]);
-      }
+      for (int i = 0; i < 2; ++i)
+        ldsm4(a[i], &As[buf][wm + 16 * i + (lane & 7) + ((lane >> 3) & 1) * 8][kk + (lane >> 4) * 8]);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        unsigned b[2];
-        b[0] = *reinterpret_cast<const unsigned*>(&Bg[buf][wn + 8 * j + g][kk + 2 * tg]);
-        b[1] = *reinterpret_cast<const unsigned*>(&Bg[buf][wn + 8 * j + g][kk + 2 * tg + 8]);
-        mma_bf16_16816(acc[0][j], a[0], b);
-        mma_bf16_16816(acc[1][j], a[1], b);
+      for (int j = 0; j < 4; j += 2) {
+        unsigned b[4];
+        ldsm4(b, &Bg[buf][wn + 8 * (j + (lane >> 4)) + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+        mma_bf16_16816(acc[0][j], a[0], *reinterpret_cast<const unsigned(*)[2]>(&b[0]));
+        mma_bf16_16816(acc[1][j], a[1], *reinterpret_cast<const unsigned(*)[2]>(&b[0]));
+        mma_bf16_16816(acc[0][j + 1], a[0], *reinterpret_cast<const unsigned(*)[2]>(&b[2]));
+        mma_bf16_16816(acc[1][j + 1], a[1], *reinterpret_cast<const unsigned(*)[2]>(&b[2]));
         if (kGlu) {
-          b[0] = *reinterpret_cast<const unsigned*>(&Bu[buf][wn + 8 * j + g][kk + 2 * tg]);
-          b[1] = *reinterpret_cast<const unsigned*>(&Bu[buf][wn + 8 * j + g][kk + 2 * tg + 8]);
-          mma_bf16_16816(accu[0][j], a[0], b);
-          mma_bf16_16816(accu[kGlu ? 1 : 0][j], a[1], b);
+          ldsm4(b, &Bu[buf][wn + 8 * (j + (lane >> 4)) + (lane & 7)][kk + ((lane >> 3) & 1) * 8]);
+          mma_bf16_16816(accu[0][j], a[0], *reinterpret_cast<const unsigned(*)[2]>(&b[0]));
+          mma_bf16_16816(accu[kGlu ? 1 : 0][j], a[1], *reinterpret_cast<const unsigned(*)[2]>(&b[0]));
+          mma_bf16_16816(accu[0][j + 1], a[0], *reinterpret_cast<const unsigned(*)[2]>(&b[2]));
+          mma_bf16_16816(accu[kGlu ? 1 : 0][j + 1], a[1], *reinterpret_cast<const unsigned(*)[2]>(&b[2]));
         }
       }
     }
