@@ -49,6 +49,7 @@ class KvNeed:
     head_dim: int
     window: Optional[int] = None  # keys a query sees, itself included; None = all
     planes: int = 2               # 2: keys and values; 1: one tensor per position that serves as both (a latent)
+    keep_first: int = 0           # with a window: the first positions of a sequence that stay visible behind it (their pages stay)
 
 
 @dataclasses.dataclass(frozen=True)
@@ -367,11 +368,12 @@ class CacheManager:
             if g.window is None:
                 continue
             first = self._first_needed_page(g, r.num_tokens)
+            kept = self.pages_for(g.need.keep_first)      # the pages of a sequence's kept first positions are never given back
             table = r.tables[gi]
-            dead = [p for p in table[:first] if p != RELEASED]
+            dead = [p for p in table[kept:first] if p != RELEASED]
             if dead:
                 g.pool.release(dead)
-                for i in range(min(first, len(table))):
+                for i in range(kept, min(first, len(table))):
                     table[i] = RELEASED
 
     def close(self, request_id: Hashable) -> None:

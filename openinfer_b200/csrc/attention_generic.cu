@@ -2,7 +2,8 @@
 // number of heads and groups, an optional window, float32 or bfloat16 storage; prompt portions
 // and single decoded tokens alike. One warp per (token, query head).
 //
-// s[i,j] = (q_i . k_j) * scale for j <= pos_i (and j > pos_i - window), online softmax in float32,
+// s[i,j] = (q_i . k_j) * scale for j <= pos_i (and j > pos_i - window, or j among the sequence's kept first keys),
+// online softmax in float32,
 // o_i = sum_j p[i,j] v_j; query head h reads kv head h / (nq / nkv)
 // (pegainfer-kernels/csrc/shared/paged_attention.cu:439-567; pegainfer-kernels/src/ops/attention.rs:507).
 // The keys of a request are visited in position order, 32 at a time, whatever else is in the
@@ -78,10 +79,14 @@ __global__ void attention_generic_kernel(
   const float slope = mods.slopes ? mods.slopes[head] : 0.f;
   const float cap = mods.softcap, inv_cap = cap > 0.f ? 1.f / cap : 0.f;
 
-  for (int base = first; base <= pos; base += 32) {
+  // the keys a row sees: [first, pos], and with kept first keys also [0, min(keep_first, first)) behind the window
+  const int kept_end = mods.keep_first > 0 ? min(mods.keep_first, first) : 0;
+  for (int seg = kept_end > 0 ? 0 : 1; seg < 2; ++seg) {
+  const int seg_lo = seg == 0 ? 0 : first, seg_hi = seg == 0 ? kept_end : pos + 1;
+  for (int base = seg_lo; base < seg_hi; base += 32) {
     const int j = base + lane;
     float s = -INFINITY;
-    if (j <= pos) {
+    if (j < seg_hi) {
       const int page = bt[j / page_size];
       const T* kp = k_cache + (size_t)page * page_stride + (size_t)(j % page_size) * row_elems + (size_t)kvh * hd;
       float dot = 0.f;
@@ -96,12 +101,12 @@ __global__ void attention_generic_kernel(
       s -= slope * (float)(pos - j);
     }
     const float m_new = fmaxf(m, warp_max(s));
-    const float p = (j <= pos) ? expf(s - m_new) : 0.f;
+    const float p = (j < seg_hi) ? expf(s - m_new) : 0.f;
     const float corr = expf(m - m_new);  // m = -inf on the first tile gives 0
     l = l * corr + warp_sum(p);
 #pragma unroll
     for (int r = 0; r < kAccs; ++r) acc[r] *= corr;
-    const int n_valid = min(32, pos - base + 1);
+    const int n_valid = min(32, seg_hi - base);
     for (int jj = 0; jj < n_valid; ++jj) {
       const float pj = __shfl_sync(0xffffffffu, p, jj);
       const int jv = base + jj;
@@ -114,6 +119,7 @@ __global__ void attention_generic_kernel(
       }
     }
     m = m_new;
+  }
   }
   T* op = out + (size_t)token * out_row_stride + (size_t)head * hd;
   const float inv_l = 1.f / l;

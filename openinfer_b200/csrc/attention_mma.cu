@@ -1028,7 +1028,7 @@ int launch_tiles(const AttnParams& p, int num_items, cudaStream_t s) {
 }
 
 bool has_mods(const AttnParams& p) {
-  return p.mods.sinks || p.mods.slopes || p.mods.softcap > 0.f || p.mods.qt_every > 0;
+  return p.mods.sinks || p.mods.slopes || p.mods.softcap > 0.f || p.mods.qt_every > 0 || p.mods.keep_first > 0;
 }
 
 template <int HD>

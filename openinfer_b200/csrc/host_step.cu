@@ -187,7 +187,7 @@ OI_API int oi_attention_layer(const OiAttnStep* s, const OiAttnLayer* l, void* s
   const int tokens = s->tokens;
   if (tokens == 0) return OI_OK;
   const bool fused = l->rope_mode == 1 && s->tensor_core && s->fuse_rope && !l->interleaved;
-  OI_REQUIRE(!(fused && (l->mods.sinks || l->mods.slopes || l->mods.softcap > 0.f || l->mods.qt_every > 0)),
+  OI_REQUIRE(!(fused && (l->mods.sinks || l->mods.slopes || l->mods.softcap > 0.f || l->mods.qt_every > 0 || l->mods.keep_first > 0)),
              "attention_layer: a step with the rotation fused into the decode kernel cannot modify its scores");
   OI_REQUIRE(l->qkv && l->out && l->k_cache && l->v_cache && s->block_table && s->kv_lens && s->cu_seqlens,
              "attention_layer: a tensor of the step or of the layer is missing");
@@ -212,7 +212,7 @@ OI_API int oi_attention_layer(const OiAttnStep* s, const OiAttnLayer* l, void* s
                                     l->norm_dtype, l->eps, l->w_offset, l->cos_tab, l->sin_tab, l->rot_half, l->max_pos,
                                     s->positions, s->slot_mapping, l->write_kv, stream);
   }
-  const OiScoreMods* mods = (l->mods.sinks || l->mods.slopes || l->mods.softcap > 0.f || l->mods.qt_every > 0) ? &l->mods : nullptr;
+  const OiScoreMods* mods = (l->mods.sinks || l->mods.slopes || l->mods.softcap > 0.f || l->mods.qt_every > 0 || l->mods.keep_first > 0) ? &l->mods : nullptr;
   if (s->num_tile_items && s->use_tcgen05 && !mods)
     OI_TRY(oi_attention_tcgen05(l->qkv, l->q_row_stride, tokens, l->out, l->out_row_stride, l->k_cache, l->v_cache,
                                 s->page_stride, s->page_size, s->num_pages, s->block_table, s->bt_stride, s->cu_seqlens,

@@ -1,7 +1,10 @@
 // Routed experts: a feed-forward of `experts` small gated layers of which every row uses `top`.
 //
 //   1. moe_router_kernel   z = W_r x in float32 (one block a row), the `top` largest logits (ties to the lower index),
-//                          their softmax -> ids [rows, top], weights [rows, top]
+//                          their softmax -> ids [rows, top], weights [rows, top]. Scoring 1 ("sigmoid, corrected, by groups"):
+//                          s = sigmoid(z); the choice goes by s + correction, among the experts of the `keep_groups` best of
+//                          `n_groups` equal groups of neighbours (a group's score: the sum of its two largest choice scores);
+//                          the weights are the chosen experts' s divided by their sum (+ 1e-20)
 //   2. moe_group_kernel    the (row, choice) pairs sorted by expert (stable, so the order never depends on timing), and
 //                          the list of row tiles (expert, first sorted place, rows) the products run over
 //   3. moe_gemm_kernel     per tile: act(x W_gate_e^T, x W_up_e^T) for the rows of the tile, gathered by their pair's row;
@@ -23,12 +26,15 @@ constexpr int kMaxTop = 32;
 
 template <typename T>
 __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const void* __restrict__ w, int w_dtype, int rows, int K,
-                                  int E, int top, int* __restrict__ ids, float* __restrict__ wts) {
+                                  int E, int top, int* __restrict__ ids, float* __restrict__ wts, int scoring,
+                                  const float* __restrict__ correction, int n_groups, int keep_groups) {
   pdl_start();
-  extern __shared__ float smem[];              // the row's logits [E], then which of them are taken [E bytes]
+  extern __shared__ float smem[];              // the row's logits [E], scores [E], group scores [E], then which are taken [E bytes]
   const int warps = blockDim.x >> 5, wi = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float* z = smem;
-  unsigned char* taken = reinterpret_cast<unsigned char*>(smem + E);
+  float* sc = smem + E;
+  float* gs = smem + 2 * E;
+  unsigned char* taken = reinterpret_cast<unsigned char*>(smem + 3 * E);
   const int row = blockIdx.x;
   const T* xr = x + (size_t)row * ldx;
   constexpr int kVec = 16 / (int)sizeof(T);
@@ -72,6 +78,46 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
   }
   __syncthreads();
   if (wi != 0) return;
+  if (scoring == 1) {
+    for (int e = lane; e < E; e += 32) {
+      const float sg = 1.f / (1.f + expf(-z[e]));
+      sc[e] = sg;
+      z[e] = sg + (correction ? correction[e] : 0.f);
+    }
+    __syncwarp();
+    if (n_groups > 1 && keep_groups < n_groups) {
+      const int per = E / n_groups;
+      for (int g = lane; g < n_groups; g += 32) {
+        float a = -INFINITY, b = -INFINITY;          // the group's two largest choice scores
+        for (int i = 0; i < per; ++i) {
+          const float v = z[g * per + i];
+          if (v > a) { b = a; a = v; } else if (v > b) { b = v; }
+        }
+        gs[g] = per > 1 ? a + b : a;
+      }
+      __syncwarp();
+      for (int e = lane; e < E; e += 32) taken[e] = 1;
+      __syncwarp();
+      for (int kept = 0; kept < keep_groups; ++kept) {
+        float best = -INFINITY;
+        int bg = 0x7fffffff;
+        for (int g = lane; g < n_groups; g += 32) {
+          const float v = gs[g];
+          if (v > -INFINITY && (bg == 0x7fffffff || v > best)) { best = v; bg = g; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+          const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+          const int og = __shfl_xor_sync(0xffffffffu, bg, o);
+          if (og != 0x7fffffff && (bg == 0x7fffffff || ov > best || (ov == best && og < bg))) { best = ov; bg = og; }
+        }
+        if (bg == 0x7fffffff) break;
+        for (int i = lane; i < per; i += 32) taken[bg * per + i] = 0;
+        if (lane == 0) gs[bg] = -INFINITY;
+        __syncwarp();
+      }
+    }
+  }
   float chosen_z[kMaxTop];
   int chosen_e[kMaxTop];
   for (int j = 0; j < top; ++j) {
@@ -99,7 +145,14 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
     chosen_z[j] = best;
     chosen_e[j] = be;
   }
-  if (lane == 0) {
+  if (lane == 0 && scoring == 1) {
+    float sum = 0.f;
+    for (int j = 0; j < top; ++j) sum += sc[chosen_e[j]];
+    for (int j = 0; j < top; ++j) {
+      ids[(size_t)row * top + j] = chosen_e[j];
+      wts[(size_t)row * top + j] = sc[chosen_e[j]] / (sum + 1e-20f);
+    }
+  } else if (lane == 0) {
     float mx = chosen_z[0], sum = 0.f;
     for (int j = 1; j < top; ++j) mx = fmaxf(mx, chosen_z[j]);
     for (int j = 0; j < top; ++j) {
@@ -568,18 +621,36 @@ OI_API int oi_moe_small(int pairs, int experts) { return pairs <= 2 * experts &&
 
 // x [rows, K] (row stride ldx) in `dtype`; router weights [E, K]; ids, wts [rows, top]; sorted [rows * top];
 // tile_info [3 * max_tiles + 1] with max_tiles = oi_moe_max_tiles(rows * top, E).
+OI_API int oi_moe_route_scored(const void* x, int dtype, long long ldx, const void* w_router, int w_dtype, int rows, int K, int E,
+                               int top, int scoring, const float* correction, int n_groups, int keep_groups, int* ids, float* wts,
+                               int* sorted, int* tile_info, void* stream);
+
 OI_API int oi_moe_route(const void* x, int dtype, long long ldx, const void* w_router, int w_dtype, int rows, int K, int E, int top,
                         int* ids, float* wts, int* sorted, int* tile_info, void* stream) {
+  return oi_moe_route_scored(x, dtype, ldx, w_router, w_dtype, rows, K, E, top, 0, nullptr, 1, 1, ids, wts, sorted, tile_info, stream);
+}
+
+// scoring 0: the `top` largest logits, weighted by their softmax. scoring 1: sigmoid scores; the choice goes by score +
+// correction (float32 [E] or null) among the experts of the `keep_groups` best of `n_groups` equal groups of neighbours;
+// weights: the chosen scores (without the correction) divided by their sum.
+OI_API int oi_moe_route_scored(const void* x, int dtype, long long ldx, const void* w_router, int w_dtype, int rows, int K, int E,
+                               int top, int scoring, const float* correction, int n_groups, int keep_groups, int* ids, float* wts,
+                               int* sorted, int* tile_info, void* stream) {
   OI_REQUIRE(rows >= 0 && K > 0 && E > 0 && top > 0 && top <= E && top <= kMaxTop, "moe_route: bad sizes experts=%d top=%d (at most %d)", E,
              top, kMaxTop);
   OI_REQUIRE(E <= 4096, "moe_route: %d experts, at most 4096", E);
+  OI_REQUIRE(scoring == 0 || scoring == 1, "moe_route: unknown scoring %d", scoring);
+  OI_REQUIRE(n_groups >= 1 && keep_groups >= 1 && keep_groups <= n_groups && E % n_groups == 0 && (E / n_groups) * keep_groups >= top,
+             "moe_route: %d experts in %d groups of which %d are kept cannot give %d choices", E, n_groups, keep_groups, top);
   if (rows == 0) return OI_OK;
   cudaStream_t s = (cudaStream_t)stream;
-  const size_t smem = (size_t)E * sizeof(float) + (size_t)E + 16;
+  const size_t smem = 3 * (size_t)E * sizeof(float) + (size_t)E + 16;
   if (dtype == OI_F32)
-    oi_launch(moe_router_kernel<float>, rows, 128, smem, s, (const float*)x, ldx, w_router, w_dtype, rows, K, E, top, ids, wts);
+    oi_launch(moe_router_kernel<float>, rows, 128, smem, s, (const float*)x, ldx, w_router, w_dtype, rows, K, E, top, ids, wts, scoring,
+              correction, n_groups, keep_groups);
   else if (dtype == OI_BF16)
-    oi_launch(moe_router_kernel<bf16>, rows, 128, smem, s, (const bf16*)x, ldx, w_router, w_dtype, rows, K, E, top, ids, wts);
+    oi_launch(moe_router_kernel<bf16>, rows, 128, smem, s, (const bf16*)x, ldx, w_router, w_dtype, rows, K, E, top, ids, wts, scoring,
+              correction, n_groups, keep_groups);
   else
     OI_REQUIRE(false, "moe_route: unknown dtype code %d", dtype);
   OI_CHECK_LAUNCH();

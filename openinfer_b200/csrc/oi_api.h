@@ -37,6 +37,7 @@ typedef struct OiScoreMods {
   float softcap;         // > 0: score <- softcap * tanh(score / softcap), before the slope
   float qt_coef;         // qt_every > 0: the score of the query at position p is multiplied by
   int qt_every;          //   1 + qt_coef * ln(floor((p + 1) / qt_every) + 1), before the cap
+  int keep_first;        // > 0, with a window: the first keep_first keys of a sequence stay visible behind the window
 } OiScoreMods;
 
 #ifdef __CUDACC__
@@ -136,7 +137,8 @@ OI_API int oi_short_conv_strided(void* out, int out_dtype, long long out_stride,
 OI_API int oi_glu_act(void* out, const void* gate_up, int dtype, int rows, int inter, int block, int act, float limit,
        void* stream);
 
-// recurrent.cu: mixers with a matrix memory per head (mode 0: the mLSTM cell, 1: the gated delta rule)
+// recurrent.cu: mixers with a matrix memory per head (mode 0: the mLSTM cell, 1: the gated delta rule, 2: linear attention
+// with one fixed decay per head, p0 = the decays [H]; q, k and v get their silu there, v in place in `qkv`)
 OI_API int oi_recurrent_record(int D);
 OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q_off, int k_off, int v_off, const float*
        gates, long long ld_gates, int i_off, int f_off, const float* decay, long long ld_decay, const void* p0, const
@@ -146,6 +148,18 @@ OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q
 OI_API int oi_head_norm_gate(void* out, int out_dtype, long long ld_out, const float* o, long long ld_o, const float*
        gate, long long ld_gate, const void* w, int w_dtype, int w_stride, int tokens, int H, int V, float eps, float
        scale, void* stream);
+
+// sandwich_ops.cu: a Dynamic Tanh norm, dyt(v) = tanh(alpha v) w + b, between two sublayers of a float32 stream
+// (h += dyt(branch; post); out = dyt(h; pre), either half optional; row_idx: out is read from these rows of h), and the
+// step of an attention that adds the projections' bias (a table by position), rotates, THEN divides q and k heads by their
+// root mean square over qk_dim numbers, and stores k and v in their pages
+OI_API int oi_dyt_step(float* h, const float* branch, const void* post_alpha, const void* post_w, const void* post_b, int
+       post_dtype, const void* pre_alpha, const void* pre_w, const void* pre_b, int pre_dtype, void* out, int out_dtype,
+       const int* row_idx, int rows, int width, void* stream);
+OI_API int oi_rope_norm_store(void* qkv, int dtype, long long row_stride, int tokens, int nq, int nkv, int hd, int qk_dim,
+       const float* bias_tab, int n_tab, long long tab_stride, const float* cos_tab, const float* sin_tab, int rot_half,
+       int max_pos, int unit_norm, float eps, const int* positions, const int* slots, void* k_cache, void* v_cache,
+       long long page_stride, int page_size, int write_kv, void* stream);
 
 // hyper.cu: several residual streams
 OI_API int oi_hyper_step(float* X, int rows, int S, int W, const float* y, const float* y2, float c1, float c2, const
@@ -164,6 +178,13 @@ OI_API int oi_moe_experts(const void* x, int dtype, long long ldx, const void* w
        int W, int F, int E, int top, float limit, int glu, const int* ids, const int* sorted, const int* tile_info, const float*
        wts, void* act, float* y, float* out, const float* add, void* stream);
 
+// oi_moe_route with the way of scoring as an argument. scoring 0: the `top` largest logits weighted by their softmax.
+// scoring 1: sigmoid scores; the choice goes by score + correction (float32 [E] or null) among the experts of the
+// `keep_groups` best of `n_groups` equal groups of neighbours (a group's score: the sum of its two largest choice scores);
+// the weights are the chosen experts' scores, without the correction, divided by their sum.
+OI_API int oi_moe_route_scored(const void* x, int dtype, long long ldx, const void* w_router, int w_dtype, int rows, int K, int E,
+                               int top, int scoring, const float* correction, int n_groups, int keep_groups, int* ids, float* wts,
+                               int* sorted, int* tile_info, void* stream);
 OI_API int oi_moe_route_table(const int* token_ids, const int* table, int rows, int vocab, int E, int top, int* ids, float*
        wts, int* sorted, int* tile_info, void* stream);
 

@@ -8,6 +8,8 @@
 //   kGatedDelta (gated delta rule):  C <- diag(g) C;  d = beta (v - C^T k);  C <- C + k d^T;  o = C^T q, with k and q made
 //                                    unit vectors (1e-6 inside the root), q times q_scale, beta = sigmoid(zb) and one decay
 //                                    per key channel g = exp(-exp(A_h) softplus(a + dt))
+//   kLinearDecay (linear attention with one fixed decay per head, "lightning attention"):
+//                                    C <- lambda_h C + k v^T;  o = C^T q, with q, k and v through silu first and no other scale
 //
 // Prompts and single decoded tokens take the same two launches. A first kernel forms, for all rows at once, what does
 // not depend on earlier rows (gates, decays, unit vectors); then block (request, head, slice of value columns) walks the
@@ -20,7 +22,7 @@
 
 namespace {
 
-enum : int { kMatrixMemory = 0, kGatedDelta = 1 };
+enum : int { kMatrixMemory = 0, kGatedDelta = 1, kLinearDecay = 2 };
 constexpr int kThreads = 128;
 constexpr int kMaxRegs = 16;   // key channels a thread holds of its column
 
@@ -33,7 +35,7 @@ struct ScanArgs {
   int i_off, f_off;
   const float* decay;          // delta: a [tokens, ld_decay], head major, D each
   long long ld_decay;
-  const void* p0;              // matrix memory: bias of zi [H]; delta: dt [H * D]
+  const void* p0;              // matrix memory: bias of zi [H]; delta: dt [H * D]; linear decay: lambda [H]
   const void* p1;              // matrix memory: bias of zf [H]; delta: A [H]
   int p_dtype;
   float cap, q_scale;
@@ -56,6 +58,7 @@ __device__ __forceinline__ float softplus_f(float x) { return fmaxf(x, 0.f) + lo
 // the recurrence alone. Record of rec >= 3 D + 2 floats: keys [D], queries [D], decays [D], two scalars, padding.
 //   matrix memory: keys as they are, queries times q_scale, (no decays), the log gates i and f
 //   delta rule:    unit keys, unit queries times q_scale, g = exp(-exp(A) softplus(a + dt)), beta
+//   linear decay:  silu of the keys, silu of the queries times q_scale; the head's values get their silu in place
 template <int kMode>
 __global__ void recurrent_prepare_kernel(ScanArgs a) {
   pdl_start();
@@ -66,7 +69,15 @@ __global__ void recurrent_prepare_kernel(ScanArgs a) {
   const float* r = a.qkv + (size_t)t * a.ld_qkv;
   float* rec = a.prep + ((size_t)t * a.H + h) * a.rec;
   const float* gr = a.gates + (size_t)t * a.ld_gates;
-  if (kMode == kMatrixMemory) {
+  if (kMode == kLinearDecay) {
+    for (int d = lane; d < D; d += 32) {
+      const float k = r[a.k_off + g * D + d], q = r[a.q_off + g * D + d];
+      rec[d] = k / (1.f + expf(-k));
+      rec[D + d] = q / (1.f + expf(-q)) * a.q_scale;
+    }
+    float* v = const_cast<float*>(r) + a.v_off + (size_t)h * a.V;      // only this warp touches the head's values of the row
+    for (int c = lane; c < a.V; c += 32) v[c] = v[c] / (1.f + expf(-v[c]));
+  } else if (kMode == kMatrixMemory) {
     for (int d = lane; d < D; d += 32) {
       rec[d] = r[a.k_off + g * D + d];
       rec[D + d] = r[a.q_off + g * D + d] * a.q_scale;
@@ -165,6 +176,7 @@ __global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, in
     nn[i] = (kMode == kMatrixMemory && d < D) ? old[(size_t)D * V + d] : 0.f;
   }
   if (kMode == kMatrixMemory) m = old[(size_t)D * V + D];
+  const float lam = kMode == kLinearDecay ? load_as_f32(a.p0, a.p_dtype, h) : 0.f;
 
   // two buffers: the next chunk's records are on their way (cp.async) while this one is worked on
   const int buf_floats = chunk * (rec + kCols);
@@ -276,6 +288,18 @@ __global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, in
         const float ns = lanes_sum<kLanes>((num[0] + num[1]) + (num[2] + num[3]));
         const float qs = lanes_sum<kLanes>((nq[0] + nq[1]) + (nq[2] + nq[3]));
         o = ns / (fmaxf(fabsf(qs), expf(-m)) + 1e-6f);
+      } else if (kMode == kLinearDecay) {
+        // the read-out does not feed the state: the chain from row to row is one multiply-add a register
+        float k[R], q[R];
+        load_channels<kLanes, R, kVec4>(k, r, D, j);
+        load_channels<kLanes, R, kVec4>(q, r + D, D, j);
+        float num[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+          C[i] = fmaf(lam, C[i], k[i] * v);
+          num[i & 3] += C[i] * q[i];
+        }
+        o = lanes_sum<kLanes>((num[0] + num[1]) + (num[2] + num[3]));
       } else {
         const float beta = r[3 * D];
         float k[R], g[R], q[R];
@@ -338,14 +362,15 @@ __global__ void head_norm_gate_kernel(TO* __restrict__ out, long long ld_out, co
 OI_API int oi_recurrent_record(int D) { return (3 * D + 2 + 3) & ~3; }   // a multiple of four floats: 16-byte copies
 
 // mode 0: matrix memory (p0, p1: the two gate biases [H]); mode 1: gated delta rule (p0: dt [H * D], p1: A [H];
-// decay: a [tokens, ld_decay]). State: [slots][2][H][D * V (+ D + 1 in mode 0)] floats. prep: scratch, see above.
+// decay: a [tokens, ld_decay]); mode 2: linear attention with a fixed decay per head (p0: lambda [H]; qkv is written: the
+// values get their silu in place). State: [slots][2][H][D * V (+ D + 1 in mode 0)] floats. prep: scratch, see above.
 OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q_off, int k_off, int v_off, const float* gates,
                              long long ld_gates, int i_off, int f_off, const float* decay, long long ld_decay, const void* p0,
                              const void* p1, int p_dtype, float cap, float q_scale, float* prep, float* state,
                              long long state_stride, const int* cu_seqlens, const int* token_req, const int* state_slots,
                              const int* state_phase, float* out, long long ld_out, int tokens, int requests, int H, int G, int D,
                              int V, void* stream) {
-  OI_REQUIRE(mode == kMatrixMemory || mode == kGatedDelta, "recurrent_scan: unknown mode %d", mode);
+  OI_REQUIRE(mode == kMatrixMemory || mode == kGatedDelta || mode == kLinearDecay, "recurrent_scan: unknown mode %d", mode);
   OI_REQUIRE(requests >= 0 && tokens >= 0 && H > 0 && G > 0 && H % G == 0 && D > 0 && V > 0,
              "recurrent_scan: bad sizes H=%d G=%d D=%d V=%d", H, G, D, V);
   OI_REQUIRE(D <= 32 * kMaxRegs, "recurrent_scan: %d key channels per head, at most %d", D, 32 * kMaxRegs);
@@ -365,6 +390,7 @@ OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q
   cudaStream_t s = (cudaStream_t)stream;
   const int warps = tokens * H;
   if (mode == kMatrixMemory) oi_launch(recurrent_prepare_kernel<kMatrixMemory>, (warps + 3) / 4, 128, 0, s, a);
+  else if (mode == kLinearDecay) oi_launch(recurrent_prepare_kernel<kLinearDecay>, (warps + 3) / 4, 128, 0, s, a);
   else oi_launch(recurrent_prepare_kernel<kGatedDelta>, (warps + 3) / 4, 128, 0, s, a);
   OI_CHECK_LAUNCH();
   const int chunk = D <= 64 ? 16 : (D <= 128 ? 8 : (D <= 256 ? 4 : 2));   // rows per buffer: two buffers of at most 13 KB
@@ -390,6 +416,7 @@ OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q
     else OI_SCAN_AS(MODE, 32, 16);                    \
   } while (0)
   if (mode == kMatrixMemory) OI_SCAN(kMatrixMemory);
+  else if (mode == kLinearDecay) OI_SCAN(kLinearDecay);
   else OI_SCAN(kGatedDelta);
 #undef OI_SCAN
 #undef OI_SCAN_AS

@@ -1,0 +1,190 @@
+// Kernels of blocks that norm a sublayer's input AND its output ("sandwich" blocks) with a Dynamic Tanh norm, and of an
+// attention that rotates first and norms afterwards.
+//
+//   dyt(v; alpha, w, b) = tanh(alpha * v) * w + b       alpha a scalar tensor, w and b vectors; no mean, no variance
+//
+//   dyt_step_kernel        one pass over the float32 stream h [rows, width]:
+//                            h <- h + dyt(branch; post)      when a sublayer's result (float32) is given
+//                            out <- dyt(h; pre)              when the next sublayer's (or the head's) input is wanted, in the
+//                                                            model's type, optionally only of the rows `row_idx` names
+//                                                            (h is then left as it was: nothing reads it again)
+//                          the place of residual add + norm in a pre-norm block: ONE kernel between two sublayers.
+//   rope_norm_store_kernel one warp per (row, head) of the fused q | k | v projection (heads of `hd` numbers): adds the
+//                          row's bias (a small table indexed by the row's position, see below), turns the first
+//                          2 * rot_half numbers of q and k heads by the position's angles (pairs (d, d + rot_half)), divides
+//                          q and k heads by their root mean square over `qk_dim` numbers (after the rotation, no weight),
+//                          writes q back in place and k and v to the row's page slot.
+//
+// The bias table: a projection with a bias b that then passes a causal filter of `taps` taps (zeros before the sequence's
+// start) equals the filter of the bias-free projection plus b * (sum of the taps that fall on positions >= 0), which
+// depends on the position alone and is constant from position taps - 1 on: table[min(pos, n_tab - 1)][column].
+#include "common.cuh"
+
+namespace {
+
+constexpr int kDytThreads = 256;
+
+struct DytParams {
+  const void* alpha;   // one number
+  const void* w;       // [width]
+  const void* b;       // [width]
+  int dtype;
+};
+
+template <typename TO>
+__global__ void dyt_step_kernel(float* __restrict__ h, const float* __restrict__ branch, DytParams post, DytParams pre,
+                                TO* __restrict__ out, const int* __restrict__ row_idx, int width) {
+  pdl_start();
+  const int r = blockIdx.x;
+  const int row = row_idx ? row_idx[r] : r;
+  float* hr = h + (size_t)row * width;
+  const float a_post = branch ? load_as_f32(post.alpha, post.dtype, 0) : 0.f;
+  const float a_pre = out ? load_as_f32(pre.alpha, pre.dtype, 0) : 0.f;
+  for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < width; c += gridDim.y * blockDim.x * 4) {
+    float v[4];
+    const bool vec = c + 4 <= width && (width & 3) == 0;
+    if (vec) {
+      const float4 t = *reinterpret_cast<const float4*>(hr + c);
+      v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
+    } else {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) v[e] = c + e < width ? hr[c + e] : 0.f;
+    }
+    if (branch) {
+      const float* br = branch + (size_t)row * width;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (c + e < width)
+          v[e] += tanhf(a_post * br[c + e]) * load_as_f32(post.w, post.dtype, c + e) + load_as_f32(post.b, post.dtype, c + e);
+      if (row_idx) {
+        // gathered rows: the stream is not read again, the sum stays in registers
+      } else if (vec) {
+        *reinterpret_cast<float4*>(hr + c) = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c + e < width) hr[c + e] = v[e];
+      }
+    }
+    if (out) {
+      TO* o = out + (size_t)r * width;
+#pragma unroll
+      for (int e = 0; e < 4; ++e)
+        if (c + e < width)
+          o[c + e] = from_f32<TO>(tanhf(a_pre * v[e]) * load_as_f32(pre.w, pre.dtype, c + e) + load_as_f32(pre.b, pre.dtype, c + e));
+    }
+  }
+}
+
+constexpr int kRopeWarps = 4;
+constexpr int kRopeMaxHd = 512;
+
+template <typename T>
+__global__ void rope_norm_store_kernel(T* __restrict__ qkv, long long row_stride, int nq, int nkv, int hd, int qk_dim,
+                                       const float* __restrict__ bias_tab, int n_tab, long long tab_stride,
+                                       const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int rot_half,
+                                       int max_pos, int unit_norm, float eps, const int* __restrict__ positions,
+                                       const int* __restrict__ slots, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                       long long page_stride, int page_size, int write_kv, int tokens) {
+  pdl_start();
+  __shared__ float sh[kRopeWarps][kRopeMaxHd];
+  const int lane = threadIdx.x & 31, wi = threadIdx.x >> 5;
+  const int heads_total = write_kv ? nq + 2 * nkv : nq;
+  const long long gw = (long long)blockIdx.x * kRopeWarps + wi;
+  if (gw >= (long long)tokens * heads_total) return;       // whole warps leave; only warp-level barriers below
+  const int token = (int)(gw / heads_total), head = (int)(gw - (long long)token * heads_total);
+  const int kind = head < nq ? 0 : (head < nq + nkv ? 1 : 2);
+  T* src = qkv + (size_t)token * row_stride + (size_t)head * hd;
+  T* dst = src;
+  if (kind != 0) {
+    const int slot = slots[token];
+    if (slot < 0) return;                                    // a padding row stores nothing
+    const int kvh = kind == 1 ? head - nq : head - nq - nkv;
+    dst = (kind == 1 ? k_cache : v_cache) + (size_t)(slot / page_size) * page_stride + (size_t)(slot % page_size) * nkv * hd +
+          (size_t)kvh * hd;
+  }
+  int pos = positions[token];
+  pos = pos < 0 ? 0 : pos;
+  const float* bias = bias_tab ? bias_tab + (size_t)min(pos, n_tab - 1) * tab_stride + (size_t)head * hd : nullptr;
+  float* x = sh[wi];
+  for (int d = lane; d < hd; d += 32) x[d] = to_f32(src[d]) + (bias ? bias[d] : 0.f);
+  __syncwarp();
+  if (kind == 2) {
+    for (int d = lane; d < hd; d += 32) dst[d] = from_f32<T>(x[d]);
+    return;
+  }
+  if (rot_half > 0) {
+    const int p = pos >= max_pos ? max_pos - 1 : pos;        // admission bounds positions
+    for (int i = lane; i < rot_half; i += 32) {
+      const float c = cos_tab[(size_t)p * rot_half + i], s = sin_tab[(size_t)p * rot_half + i];
+      const float a = x[i], b = x[i + rot_half];
+      x[i] = a * c - b * s;
+      x[i + rot_half] = b * c + a * s;
+    }
+    __syncwarp();
+  }
+  float inv = 1.f;
+  if (unit_norm) {
+    float ss = 0.f;
+    for (int d = lane; d < qk_dim; d += 32) ss += x[d] * x[d];
+    ss = warp_sum(ss);
+    inv = 1.f / sqrtf(ss / (float)qk_dim + eps);
+  }
+  for (int d = lane; d < hd; d += 32) dst[d] = from_f32<T>(x[d] * inv);
+}
+
+}  // namespace
+
+// h [*, width] float32 (the stream; updated in place when `branch` is given); branch float32 [rows, width] or null;
+// out [rows, width] of `out_dtype` or null; row_idx: the rows of h (and of branch) that `out` is formed from, or null.
+// post_* / pre_*: alpha (one number), weight and bias of the two norms, all three of one dtype code each.
+OI_API int oi_dyt_step(float* h, const float* branch, const void* post_alpha, const void* post_w, const void* post_b, int post_dtype,
+                       const void* pre_alpha, const void* pre_w, const void* pre_b, int pre_dtype, void* out, int out_dtype,
+                       const int* row_idx, int rows, int width, void* stream) {
+  OI_REQUIRE(rows >= 0 && width > 0 && h != nullptr, "dyt_step: bad sizes rows=%d width=%d", rows, width);
+  OI_REQUIRE(!branch || (post_alpha && post_w && post_b), "dyt_step: a branch needs the norm of its output");
+  OI_REQUIRE(!out || (pre_alpha && pre_w && pre_b), "dyt_step: an output needs its norm");
+  OI_REQUIRE(!row_idx || out, "dyt_step: gathered rows need an output");
+  if (rows == 0 || (!branch && !out)) return OI_OK;
+  const DytParams post{post_alpha, post_w, post_b, post_dtype}, pre{pre_alpha, pre_w, pre_b, pre_dtype};
+  const int quads = (width + 3) / 4;
+  const int threads = quads >= kDytThreads ? kDytThreads : ((quads + 31) / 32) * 32;
+  const dim3 grid(rows, (quads + threads - 1) / threads);
+  cudaStream_t s = (cudaStream_t)stream;
+  if (!out || out_dtype == OI_F32)
+    oi_launch(dyt_step_kernel<float>, grid, threads, 0, s, h, branch, post, pre, (float*)out, row_idx, width);
+  else if (out_dtype == OI_BF16)
+    oi_launch(dyt_step_kernel<bf16>, grid, threads, 0, s, h, branch, post, pre, (bf16*)out, row_idx, width);
+  else
+    OI_REQUIRE(false, "dyt_step: unknown dtype code %d", out_dtype);
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}
+
+// qkv [tokens, row_stride]: heads of hd numbers, nq query heads, then (write_kv) nkv key heads and nkv value heads.
+// bias_tab float32 [n_tab, tab_stride] or null; cos / sin float32 [max_pos, rot_half] or null (rot_half 0).
+OI_API int oi_rope_norm_store(void* qkv, int dtype, long long row_stride, int tokens, int nq, int nkv, int hd, int qk_dim,
+                              const float* bias_tab, int n_tab, long long tab_stride, const float* cos_tab, const float* sin_tab,
+                              int rot_half, int max_pos, int unit_norm, float eps, const int* positions, const int* slots,
+                              void* k_cache, void* v_cache, long long page_stride, int page_size, int write_kv, void* stream) {
+  OI_REQUIRE(tokens >= 0 && nq > 0 && nkv > 0 && hd > 0 && hd <= kRopeMaxHd && qk_dim > 0 && qk_dim <= hd,
+             "rope_norm_store: bad sizes nq=%d nkv=%d hd=%d qk_dim=%d", nq, nkv, hd, qk_dim);
+  OI_REQUIRE(rot_half >= 0 && 2 * rot_half <= hd && (rot_half == 0 || (cos_tab && sin_tab && max_pos > 0)),
+             "rope_norm_store: %d rotated pairs in a head of %d numbers, or no tables", rot_half, hd);
+  OI_REQUIRE(positions && (!write_kv || (slots && k_cache && v_cache && page_size > 0)), "rope_norm_store: the step's positions and slots are missing");
+  OI_REQUIRE(!bias_tab || n_tab > 0, "rope_norm_store: an empty bias table");
+  if (tokens == 0) return OI_OK;
+  const long long warps = (long long)tokens * (write_kv ? nq + 2 * nkv : nq);
+  const unsigned blocks = (unsigned)((warps + kRopeWarps - 1) / kRopeWarps);
+  cudaStream_t s = (cudaStream_t)stream;
+#define OI_RNS(T)                                                                                                          \
+  oi_launch(rope_norm_store_kernel<T>, blocks, kRopeWarps * 32, 0, s, (T*)qkv, row_stride, nq, nkv, hd, qk_dim, bias_tab, n_tab, \
+            tab_stride, cos_tab, sin_tab, rot_half, max_pos, unit_norm, eps, positions, slots, (T*)k_cache, (T*)v_cache,    \
+            page_stride, page_size, write_kv, tokens)
+  if (dtype == OI_F32) OI_RNS(float);
+  else if (dtype == OI_BF16) OI_RNS(bf16);
+  else OI_REQUIRE(false, "rope_norm_store: unknown dtype code %d", dtype);
+#undef OI_RNS
+  OI_CHECK_LAUNCH();
+  return OI_OK;
+}

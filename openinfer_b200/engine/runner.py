@@ -230,6 +230,8 @@ class ModelRunner:
                 logits = self._step_decode_graph(entries, starts)
             else:
                 ctx, row_idx = self._build_context(entries, starts)
+                if getattr(self, "stream_probe", None) is not None:
+                    ctx.scratch["stream_probe"] = self.stream_probe    # blocks that can, append the stream behind them (tests)
                 logits = self.model.run(ctx, row_idx)
         except Exception:
             for rid in reserved:

@@ -340,6 +340,7 @@ def tcgen05_status() -> int:
 
 
 FUSE_ROPE_IN_DECODE = True
+KEPT_KEYS_ON_TENSOR_CORES = False   # windows that keep a sequence's first keys visible: the general kernel
 MODS_ON_TENSOR_CORES = True    # layers that modify their scores run on the mma.sync tile and decode kernels (False: the general kernel)
 
 
@@ -368,11 +369,13 @@ def decode_takes_rope(qkv: torch.Tensor, ctx, group_step, nq: int, nkv: int, hd:
 
 
 def attention_step(ctx, group_step, qkv: torch.Tensor, out: torch.Tensor, k_cache: torch.Tensor, page_stride: int,
-                   nq: int, nkv: int, hd: int, window, cos=None, q_norm_w=None, mods: bool = False) -> "native.AttnStep":
+                   nq: int, nkv: int, hd: int, window, cos=None, q_norm_w=None, mods: bool = False,
+                   keep_first: int = 0) -> "native.AttnStep":
     """What every attention call of one geometry shares in this step (csrc/oi_api.h, OiAttnStep): the step's metadata
     on the device, which kernels take it, and their work items. Made once per step and geometry. ``mods``: the layers of
     this geometry modify their scores (OiScoreMods), which not every kernel takes."""
-    key = ("attention_step", id(group_step), nq, nkv, hd, window, qkv.dtype, qkv.stride(0), out.stride(0), cos is not None, mods)
+    key = ("attention_step", id(group_step), nq, nkv, hd, window, qkv.dtype, qkv.stride(0), out.stride(0), cos is not None, mods,
+           keep_first)
     step = ctx.scratch.get(key)
     if step is not None:
         return step
@@ -380,7 +383,8 @@ def attention_step(ctx, group_step, qkv: torch.Tensor, out: torch.Tensor, k_cach
     bt = group_step.block_table
     # the tensor-core kernels: bfloat16, head_dim 32, 64 or 128
     tensor_core = (qkv.dtype == torch.bfloat16 and hd in (32, 64, 128) and group <= ROWS_PER_CTA_LARGE
-                   and qkv.stride(0) % 2 == 0 and page_stride % 8 == 0 and not (mods and not MODS_ON_TENSOR_CORES))
+                   and qkv.stride(0) % 2 == 0 and page_stride % 8 == 0 and not (mods and not MODS_ON_TENSOR_CORES)
+                   and not (keep_first > 0 and not KEPT_KEYS_ON_TENSOR_CORES))
     def ptr(obj, name):     # a step that only runs kernels which do not read a tensor may leave it out
         t = getattr(obj, name, None)
         return 0 if t is None else t.data_ptr()

@@ -70,6 +70,9 @@ _SIGNATURES = {
     "oi_moe_route": [P, I, L, P, I, I, I, I, I, P, P, P, P, P],
     "oi_moe_experts": [P, I, L, P, P, I, I, I, I, I, F, I, P, P, P, P, P, P, P, P, P],
     "oi_moe_route_table": [P, P, I, I, I, I, P, P, P, P, P],
+    "oi_moe_route_scored": [P, I, L, P, I, I, I, I, I, I, P, I, I, P, P, P, P, P],
+    "oi_dyt_step": [P, P, P, P, P, I, P, P, P, I, P, I, P, I, I, P],
+    "oi_rope_norm_store": [P, I, L, I, I, I, I, I, P, I, L, P, P, I, I, I, F, P, P, P, P, L, I, I, P],
     "oi_moe_small": [I, I],
     "oi_latent_rope_store": [P, L, I, I, P, L, I, I, I, I, P, I, F, F, I, P, P, I, P, P, I, I, I, I, P],
     "oi_add2_cast": [P, P, P, P, I, L, P],

@@ -46,7 +46,8 @@ class AttnStep(Structure):
 
 
 class ScoreMods(Structure):
-    _fields_ = [("sinks", c_void_p), ("slopes", c_void_p), ("softcap", c_float), ("qt_coef", c_float), ("qt_every", c_int)]
+    _fields_ = [("sinks", c_void_p), ("slopes", c_void_p), ("softcap", c_float), ("qt_coef", c_float), ("qt_every", c_int),
+                ("keep_first", c_int)]
 
 
 class AttnLayer(Structure):

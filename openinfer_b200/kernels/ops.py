@@ -524,15 +524,18 @@ def short_conv_act(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, sta
 # ---------------------------------------------------------------------------
 # recurrent mixers with a matrix memory per head (csrc/recurrent.cu)
 # ---------------------------------------------------------------------------
-SCAN_MATRIX_MEMORY, SCAN_GATED_DELTA = 0, 1
+SCAN_MATRIX_MEMORY, SCAN_GATED_DELTA, SCAN_LINEAR_DECAY = 0, 1, 2
 
 
 def recurrent_scan(mode: int, out: torch.Tensor, qkv: torch.Tensor, offsets, gates: torch.Tensor, gate_offsets, state: torch.Tensor,
-                   ctx, heads: int, kv_heads: int, dim: int, vdim: int, *, p0: torch.Tensor, p1: torch.Tensor,
+                   ctx, heads: int, kv_heads: int, dim: int, vdim: int, *, p0: torch.Tensor, p1: Optional[torch.Tensor] = None,
                    decay: Optional[torch.Tensor] = None, cap: float = 0.0, q_scale: float = 1.0) -> torch.Tensor:
     """The rows of a step through a matrix memory, request by request (see csrc/recurrent.cu). ``qkv`` and ``gates`` are
     float32 [tokens, *] buffers read at the column ``offsets`` (q, k, v) and ``gate_offsets``; ``state`` float32
-    [slots, 2, heads, elems]; ``out`` float32 [tokens, heads * vdim]."""
+    [slots, 2, heads, elems]; ``out`` float32 [tokens, heads * vdim]. ``SCAN_LINEAR_DECAY``: ``p0`` holds the heads' fixed
+    decays, q, k and v get their silu in the kernels (v in place in ``qkv``), gates and ``p1`` are not read."""
+    if p1 is None:
+        p1 = p0
     _cuda(out, qkv, gates, state, p0, p1, decay)
     for t in (out, qkv, gates, state, decay):
         if t is not None and (t.dtype != torch.float32 or t.stride(-1) != 1):
@@ -626,10 +629,18 @@ def scaled_sum(out: torch.Tensor, a: torch.Tensor, b: torch.Tensor, ca: float, c
 # ---------------------------------------------------------------------------
 # routed experts (csrc/moe.cu)
 # ---------------------------------------------------------------------------
-def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int):
+def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int, *, scoring: str = "softmax_top",
+              correction: Optional[torch.Tensor] = None, groups: int = 1, keep_groups: int = 1):
     """Router logits in float32, the ``top`` largest per row and their softmax, and the rows grouped by expert.
+    ``scoring`` "sigmoid_groups": scores sigmoid(logit); the choice goes by score + ``correction`` (float32 [experts]) among
+    the experts of the ``keep_groups`` best of ``groups`` equal groups of neighbours (a group's score: the sum of its two
+    largest choice scores); the weights are the chosen scores divided by their sum.
     Returns (ids [rows, top] int32, weights [rows, top] float32, sorted pairs, tile list): the last two feed ``moe_experts``."""
-    _cuda(x, w_router)
+    _cuda(x, w_router, correction)
+    if scoring not in ("softmax_top", "sigmoid_groups"):
+        raise KernelError(f"moe_route: unknown scoring {scoring!r}")
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != w_router.shape[0] or not correction.is_contiguous()):
+        raise KernelError("moe_route: the correction must be a contiguous float32 tensor of one number an expert")
     rows, K = x.shape
     E = w_router.shape[0]
     if x.stride(1) != 1 or not w_router.is_contiguous() or w_router.shape[1] != K:
@@ -639,9 +650,10 @@ def moe_route(x: torch.Tensor, w_router: torch.Tensor, top: int):
     wts = torch.empty((rows, top), dtype=torch.float32, device=x.device)
     order = torch.empty(rows * top, dtype=torch.int32, device=x.device)
     tiles = torch.empty(3 * L.oi_moe_max_tiles(rows * top, E) + 1, dtype=torch.int32, device=x.device)
-    _lib.check(L.oi_moe_route(x.data_ptr(), _code(x, "moe_route"), x.stride(0), w_router.data_ptr(), _code(w_router, "moe_route router"),
-                              rows, K, E, int(top), ids.data_ptr(), wts.data_ptr(), order.data_ptr(), tiles.data_ptr(), _stream()),
-               "moe_route")
+    _lib.check(L.oi_moe_route_scored(x.data_ptr(), _code(x, "moe_route"), x.stride(0), w_router.data_ptr(),
+                                     _code(w_router, "moe_route router"), rows, K, E, int(top), 1 if scoring == "sigmoid_groups" else 0,
+                                     _ptr(correction), int(groups), int(keep_groups), ids.data_ptr(), wts.data_ptr(), order.data_ptr(),
+                                     tiles.data_ptr(), _stream()), "moe_route")
     return ids, wts, order, tiles
 
 
@@ -739,3 +751,63 @@ def token_gate(g: torch.Tensor, token_ids: torch.Tensor, table: torch.Tensor, of
                                          _code(table, "token_gate table"), table.stride(0), table.shape[0], int(off), dim, tokens,
                                          _stream()), "token_gate")
     return g
+
+
+# ---------------------------------------------------------------------------
+# blocks with a norm on both sides of a sublayer; rotation before the norm (csrc/sandwich_ops.cu)
+# ---------------------------------------------------------------------------
+def dyt_step(h: torch.Tensor, *, branch: Optional[torch.Tensor] = None, post=None, pre=None, out: Optional[torch.Tensor] = None,
+             row_idx: Optional[torch.Tensor] = None) -> Optional[torch.Tensor]:
+    """One pass over the float32 stream ``h`` [rows, width] with the norm dyt(v) = tanh(alpha v) w + b:
+    h += dyt(branch; post) when ``branch`` (float32) is given, and out = dyt(h; pre) when ``out`` is. ``post`` and ``pre``
+    are (alpha, w, b) tensor triples of one dtype each. ``row_idx``: out row r is formed from row row_idx[r] (h is then
+    left unchanged). ``out`` may be ``h`` itself (the norm in place)."""
+    _cuda(h, branch, out, row_idx, *(post or ()), *(pre or ()))
+    _i32(row_idx, "dyt_step row_idx")
+    if h.dtype != torch.float32 or not h.is_contiguous() or h.dim() != 2:
+        raise KernelError("dyt_step: the stream must be contiguous float32 rows")
+    width = h.shape[1]
+    rows = h.shape[0] if row_idx is None else row_idx.numel()
+    if branch is not None and (branch.dtype != torch.float32 or branch.shape != h.shape or not branch.is_contiguous() or post is None):
+        raise KernelError("dyt_step: the branch must be float32 of the stream's shape, with the norm of its output")
+    if out is not None and (pre is None or out.shape != (rows, width) or not out.is_contiguous()):
+        raise KernelError("dyt_step: the output must be contiguous [rows, width], with its norm")
+    for trio in (post, pre):
+        if trio is not None:
+            a, w, b = trio
+            if not (a.dtype == w.dtype == b.dtype) or a.numel() != 1 or w.numel() != width or b.numel() != width \
+                    or not (w.is_contiguous() and b.is_contiguous()):
+                raise KernelError("dyt_step: a norm is one number, a weight and a bias of the stream's width, of one dtype")
+    pa, pw, pb = post if post is not None else (None, None, None)
+    ra, rw, rb = pre if pre is not None else (None, None, None)
+    _lib.check(_lib.load().oi_dyt_step(h.data_ptr(), _ptr(branch), _ptr(pa), _ptr(pw), _ptr(pb), _code(pw, "dyt_step") if pw is not None else 0,
+                                       _ptr(ra), _ptr(rw), _ptr(rb), _code(rw, "dyt_step") if rw is not None else 0, _ptr(out),
+                                       _code(out, "dyt_step") if out is not None else 0, _ptr(row_idx), rows, width, _stream()), "dyt_step")
+    return out
+
+
+def rope_norm_store(qkv: torch.Tensor, nq: int, nkv: int, hd: int, qk_dim: int, *, bias_tab: Optional[torch.Tensor],
+                    cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], unit_norm: bool, eps: float, positions: torch.Tensor,
+                    slots: Optional[torch.Tensor], k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor], page_stride: int,
+                    page_size: int, write_kv: bool) -> None:
+    """The fused q | k | v rows (heads of ``hd`` numbers) of a step: add ``bias_tab[min(position, last)]`` (float32
+    [n, >= columns]), turn the first 2 * cos.shape[1] numbers of q and k heads (pairs (d, d + half)), then, with
+    ``unit_norm``, divide q and k heads by their root mean square over ``qk_dim`` numbers; q is written back in place, k and
+    v (``write_kv``) go to the rows' page slots."""
+    _cuda(qkv, bias_tab, cos, sin, positions, slots, k_cache, v_cache)
+    _i32(positions, "rope_norm_store positions")
+    _i32(slots, "rope_norm_store slots")
+    cols = (nq + (2 * nkv if write_kv else 0)) * hd
+    if qkv.stride(1) != 1 or qkv.shape[1] < cols:
+        raise KernelError(f"rope_norm_store: rows of {qkv.shape[1]} numbers for {cols} columns")
+    if bias_tab is not None and (bias_tab.dtype != torch.float32 or bias_tab.dim() != 2 or bias_tab.shape[1] < cols or bias_tab.stride(1) != 1):
+        raise KernelError("rope_norm_store: the bias table must be float32 [n, columns]")
+    if cos is not None and (cos.dtype != torch.float32 or sin is None or sin.shape != cos.shape or not (cos.is_contiguous() and sin.is_contiguous())):
+        raise KernelError("rope_norm_store: cos / sin must be contiguous float32 tables of one shape")
+    if write_kv and (k_cache is None or v_cache is None or k_cache.dtype != qkv.dtype or v_cache.dtype != qkv.dtype):
+        raise KernelError("rope_norm_store: the cache must have the rows' dtype")
+    _lib.check(_lib.load().oi_rope_norm_store(
+        qkv.data_ptr(), _code(qkv, "rope_norm_store"), qkv.stride(0), qkv.shape[0], nq, nkv, hd, qk_dim, _ptr(bias_tab),
+        0 if bias_tab is None else bias_tab.shape[0], 0 if bias_tab is None else bias_tab.stride(0), _ptr(cos), _ptr(sin),
+        0 if cos is None else cos.shape[1], 0 if cos is None else cos.shape[0], 1 if unit_norm else 0, float(eps), positions.data_ptr(),
+        _ptr(slots), _ptr(k_cache), _ptr(v_cache), int(page_stride), int(page_size), 1 if write_kv else 0, _stream()), "rope_norm_store")

@@ -1,2 +1,2 @@
 """Built-in architectures. Importing this package registers them."""
-from . import bubalix, delunex, pilonex, qwen3  # noqa: F401
+from . import bubalix, delunex, luzitar, pilonex, qwen3  # noqa: F401

@@ -19,6 +19,13 @@ position; a cap on the scores (cap * tanh(s / cap)); a distance bias slope_h * (
 a learned sink per head in the softmax's denominator; a sigmoid gate per head on the attention's output, read off the
 mixer's input by rows appended to the fused projection. Temperature, cap, bias and sink are applied to the float32 scores
 inside the attention kernels (csrc/oi_api.h, OiScoreMods).
+
+Also from the spec: biases on q, k and v; a unit norm of q and k heads AFTER the rotation (root mean square over qk_dim
+numbers, no weight) instead of the weighted norm before it; with a window, a number of first keys of the sequence that stay
+visible behind it (their pages are kept). A layer with biases or the norm behind the rotation prepares its rows with one
+kernel of its own (csrc/sandwich_ops.cu: bias, rotation, norm, cache write) and hands the attention kernels ready queries.
+A bias in front of the filter is carried behind it: filter(u + b)_t = filter(u)_t + b * (sum of the taps that fall on
+positions >= 0), a small table by position that the same kernel adds.
 """
 from __future__ import annotations
 
@@ -63,7 +70,18 @@ class Attention(Mixer):
         self.qkv_cols = self.q_dim + 2 * self.kv_dim
         self.gate_off = self.qkv_cols                      # the gate's columns of the fused projection, behind q | k | v
         self.in_cols = -(-(self.qkv_cols + (s.num_heads if s.head_gate else 0)) // 8) * 8
-        self.has_mods = bool(s.sink or s.score_cap > 0.0 or s.distance_slope_exponent > 0.0 or s.q_temperature is not None)
+        if s.keep_first < 0 or s.unit_norm_after_rotation_eps < 0.0:
+            raise ValueError("attention: keep_first and the unit norm's eps cannot be negative")
+        if s.unit_norm_after_rotation_eps > 0.0 and s.qk_norm is not None:
+            raise ValueError("attention: q and k are normed before the rotation or behind it, not both")
+        self.keep_first = int(s.keep_first) if s.window else 0
+        # rows prepared by rope_norm_store (bias, rotation, unit norm, cache write) instead of the norm-then-rotate kernel
+        self.own_prepare = bool(s.qkv_bias or s.unit_norm_after_rotation_eps > 0.0)
+        if self.own_prepare and s.position.kind != "none" and getattr(s.position, "interleaved", False):
+            raise ValueError("attention: the rotation in front of a unit norm turns the pairs (d, d + half)")
+        self.bias_tab: Optional[torch.Tensor] = None
+        self.has_mods = bool(s.sink or s.score_cap > 0.0 or s.distance_slope_exponent > 0.0 or s.q_temperature is not None
+                             or self.keep_first > 0)
         self.w_conv: Optional[torch.Tensor] = None
         self.sinks: Optional[torch.Tensor] = None
         self.slopes: Optional[torch.Tensor] = None
@@ -76,7 +94,7 @@ class Attention(Mixer):
 
     def kv_need(self) -> Optional[KvNeed]:
         s = self.spec
-        return KvNeed(s.num_kv_heads, s.head_dim, s.window)
+        return KvNeed(s.num_kv_heads, s.head_dim, s.window, keep_first=self.keep_first)
 
     def state_needs(self):
         s = self.spec
@@ -101,6 +119,9 @@ class Attention(Mixer):
             p[s.sink_name] = ParamInfo((s.num_heads,), ("normal", 1.0))
         if s.head_gate:
             p[s.gate_name] = ParamInfo((s.num_heads, s.hidden_size), ("normal", s.hidden_size ** -0.5))
+        if s.qkv_bias:
+            for name, rows in ((s.q_name, s.num_heads * self.qk), (s.k_name, s.num_kv_heads * self.qk), (s.v_name, s.num_kv_heads * self.vd)):
+                p[name + s.bias_suffix] = ParamInfo((rows,), ("normal", 0.1))
         return p
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -131,6 +152,17 @@ class Attention(Mixer):
             self.w_conv = torch.cat([rows_padded(tensors[n + s.conv_suffix], heads, size) for n, heads, size in names], dim=0).contiguous()
         if s.sink:
             self.sinks = tensors[s.sink_name].to(torch.float32).contiguous()
+        if s.qkv_bias:
+            # the bias as the filter hands it on, by position: row m holds b * (sum of the taps j >= taps - 1 - m), the last
+            # row b * (sum of all taps); without a filter the one row b
+            names = ((s.q_name, s.num_heads, self.qk), (s.k_name, s.num_kv_heads, self.qk), (s.v_name, s.num_kv_heads, self.vd))
+            b = torch.cat([rows_padded(tensors[n + s.bias_suffix].to(torch.float64)[:, None], heads, size)[:, 0] for n, heads, size in names])
+            if s.conv_taps > 0:
+                w = self.w_conv.to(torch.float64)
+                tab = torch.stack([b * w[:, s.conv_taps - 1 - m:].sum(dim=1) for m in range(s.conv_taps)])
+            else:
+                tab = b[None, :]
+            self.bias_tab = tab.to(torch.float32).contiguous()
         o = tensors[s.o_name]
         if self.vd != hd:
             wide = torch.zeros((o.shape[0], s.num_heads, hd), dtype=o.dtype, device=o.device)
@@ -160,7 +192,8 @@ class Attention(Mixer):
             coef, every = s.q_temperature if s.q_temperature is not None else (0.0, 0)
             self.mods = native.ScoreMods(sinks=None if self.sinks is None else self.sinks.data_ptr(),
                                          slopes=None if self.slopes is None else self.slopes.data_ptr(),
-                                         softcap=float(s.score_cap), qt_coef=float(coef), qt_every=int(every))
+                                         softcap=float(s.score_cap), qt_coef=float(coef), qt_every=int(every),
+                                         keep_first=self.keep_first)
 
     takes_out_dtype = True
 
@@ -186,10 +219,26 @@ class Attention(Mixer):
         cos, sin = self.tables if self.tables is not None else (None, None)
         qn = s.qk_norm
         out = torch.empty((x.shape[0], self.q_dim), dtype=x.dtype, device=x.device)
+        if self.own_prepare:
+            # bias, rotation, unit norm and cache write in one kernel of the layer's own; the attention kernels get ready rows
+            ops.rope_norm_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.qk, bias_tab=self.bias_tab, cos=cos, sin=sin,
+                                unit_norm=s.unit_norm_after_rotation_eps > 0.0, eps=s.unit_norm_after_rotation_eps,
+                                positions=ctx.positions, slots=group.slot_mapping if binding.owns_kv else None,
+                                k_cache=k_cache if binding.owns_kv else None, v_cache=v_cache if binding.owns_kv else None,
+                                page_stride=page_stride, page_size=ctx.cache.page_size, write_kv=binding.owns_kv)
+            step = attn_kernels.attention_step(ctx, group, qkv, out, k_cache, page_stride, s.num_heads, s.num_kv_heads,
+                                               s.head_dim, s.window, mods=self.has_mods, keep_first=self.keep_first)
+            layer = attn_kernels.attention_layer(qkv, out, k_cache, v_cache, s.num_heads, s.num_kv_heads, s.head_dim, self.scale,
+                                                 s.window, write_kv=False, rope_mode=0, mods=self.mods)
+            attn_kernels.run_attention(step, layer)
+            if s.head_gate:
+                ops.head_gate(out, raw[:, self.gate_off: self.gate_off + s.num_heads], s.num_heads, s.head_dim)
+            return linear(out, self.w_o, out_dtype=out_dtype)
         # One native call: the norm + rotation + cache write (in a kernel of its own, or inside the decode kernel when
         # the step is single tokens in one wave), then the attention kernel(s) that take the step's shape.
         step = attn_kernels.attention_step(ctx, group, qkv, out, k_cache, page_stride, s.num_heads, s.num_kv_heads,
-                                           s.head_dim, s.window, cos=cos, q_norm_w=self.q_norm_w, mods=self.has_mods)
+                                           s.head_dim, s.window, cos=cos, q_norm_w=self.q_norm_w, mods=self.has_mods,
+                                           keep_first=self.keep_first)
         layer = attn_kernels.attention_layer(
             qkv, out, k_cache, v_cache, s.num_heads, s.num_kv_heads, s.head_dim, self.scale, s.window,
             q_norm_w=self.q_norm_w, k_norm_w=self.k_norm_w, eps=qn.eps * self.norm_eps_factor if qn else 0.0,

@@ -279,3 +279,84 @@ class HyperBlock(Block):
             m = self.feed_forward.forward(x, ctx, out_dtype=torch.float32)
             pending = PendingBranch(m, self.ff_streams)
         return h, pending
+
+
+@dataclasses.dataclass
+class PendingNormed:
+    """A sublayer's result (float32) that has not reached the stream yet, and the norm it passes on its way there. The
+    kernel that opens the next sublayer (also the next block's first), or the final norm, carries it out."""
+
+    y: torch.Tensor
+    norm: Part
+
+
+@register_block("sandwich")
+class SandwichBlock(Block):
+    """x <- x + out_norm(mixer(in_norm(x))), then x <- x + out_norm'(ff(in_norm'(x))): a norm before AND behind each
+    sublayer, four norms a layer (``input_norm`` / ``mixer_out_norm``, ``post_norm`` / ``feed_forward_out_norm``), all Dynamic
+    Tanh. The feed-forward is optional.
+
+    The stream is float32 whatever the model's type. ONE elementwise kernel stands between two sublayers: it norms the
+    finished sublayer's result, adds it to the stream and forms the next sublayer's normed input in the model's type
+    (csrc/sandwich_ops.cu), across the border between two blocks too: the block hands its last result on as a
+    ``PendingNormed``. With ``ctx.scratch["stream_probe"]`` (a list) the block joins its last result at once and appends a
+    copy of the stream, so that a test can look at the stream behind every layer."""
+
+    stream_dtype = torch.float32
+
+    def __init__(self, spec: BlockSpec) -> None:
+        super().__init__(spec)
+        from .norm import DynamicTanh
+        self._mixer = build_mixer(spec.mixer)
+        self.feed_forward = build_feed_forward(spec.feed_forward) if spec.feed_forward is not None else None
+        self.input_norm = build_norm(spec.input_norm)
+        self.mixer_out_norm = build_norm(spec.mixer_out_norm)
+        self.post_norm = build_norm(spec.post_norm) if self.feed_forward is not None else None
+        self.ff_out_norm = build_norm(spec.feed_forward_out_norm) if self.feed_forward is not None else None
+        for n in (self.input_norm, self.mixer_out_norm, self.post_norm, self.ff_out_norm):
+            if n is not None and not isinstance(n, DynamicTanh):
+                raise ValueError("a sandwich block needs dyt norms")
+        for part in (self._mixer, self.feed_forward):
+            if part is not None and not getattr(part, "takes_out_dtype", False):
+                raise ValueError(f"a sandwich block needs parts that can return float32, {type(part).__name__} cannot")
+
+    @property
+    def mixer(self):
+        return self._mixer
+
+    def sub_parts(self) -> Dict[str, Part]:
+        s = self.spec
+        parts: Dict[str, Part] = {s.input_norm_name: self.input_norm, s.mixer_name: self._mixer,
+                                  s.mixer_out_norm_name: self.mixer_out_norm}
+        if self.feed_forward is not None:
+            parts[s.post_norm_name] = self.post_norm
+            parts[s.feed_forward_name] = self.feed_forward
+            parts[s.feed_forward_out_norm_name] = self.ff_out_norm
+        return parts
+
+    @staticmethod
+    def open_sublayer(h: torch.Tensor, pending: Optional[PendingNormed], norm, dtype: torch.dtype) -> torch.Tensor:
+        """The pending result reaches the stream through its norm, and the next sublayer's input comes off the stream
+        through ``norm``: one kernel."""
+        out = torch.empty(h.shape, dtype=dtype, device=h.device)
+        ops.dyt_step(h, branch=pending.y if pending is not None else None, post=pending.norm.triple() if pending is not None else None,
+                     pre=norm.triple(), out=out)
+        return out
+
+    def forward(self, h: torch.Tensor, pending, ctx, binding: CacheBinding):
+        if h.dtype != torch.float32 or h.dim() != 2:
+            raise RuntimeError("a sandwich block takes one float32 stream")
+        if pending is not None and not isinstance(pending, PendingNormed):
+            raise RuntimeError("a sandwich block follows sandwich blocks only")
+        dtype = ctx.scratch["model_dtype"]
+        x = self.open_sublayer(h, pending, self.input_norm, dtype)
+        pending = PendingNormed(self._mixer.forward(x, ctx, binding, out_dtype=torch.float32), self.mixer_out_norm)
+        if self.feed_forward is not None:
+            x = self.open_sublayer(h, pending, self.post_norm, dtype)
+            pending = PendingNormed(self.feed_forward.forward(x, ctx, out_dtype=torch.float32), self.ff_out_norm)
+        probe = ctx.scratch.get("stream_probe")
+        if probe is not None:
+            ops.dyt_step(h, branch=pending.y, post=pending.norm.triple())
+            probe.append(h.clone())
+            pending = None
+        return h, pending

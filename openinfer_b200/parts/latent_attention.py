@@ -18,6 +18,10 @@ norms the latent, turns the key part, stores both, and turns the heads' query pa
 head in the softmax's denominator) is applied by the attention kernels; a gate per OUTPUT NUMBER (``gate_per`` "element")
 sits between the value up-projection and the output projection, so the former then runs in every step.
 
+A position encoding that turns neighbours (2 n, 2 n + 1) (``PositionSpec.interleaved``) costs nothing at run time: the rows
+of the query projection's rotated part and of the down-projection's key part are reordered once, when the weights are
+loaded, so that pair n sits at (n, n + rope_dim / 2); a dot product does not change when both sides are reordered alike.
+
 A layer without a latent of its own (``has_latent`` False) reads the pages another layer wrote, with its own queries,
 up-projections, window and gate.
 """
@@ -115,11 +119,15 @@ class LatentAttention(Mixer):
         uk = wuk.to(f64).view(H, D, R)
         uv = wuv.to(f64).view(H, V, R)
         P = s.rope_dim
+        # where the rotated numbers go: as stored, or (interleaved pairs) evens first, then odds
+        turn = torch.arange(P, device=dev)
+        if P and s.position is not None and s.position.interleaved:
+            turn = torch.cat([torch.arange(0, P, 2, device=dev), torch.arange(1, P, 2, device=dev)])
         if s.absorb == "weights":
             wq_heads = wq.to(f64).view(H, D + P, W)
             q_rows = torch.zeros((H, row, W), dtype=f64, device=dev)
             q_rows[:, :R] = torch.matmul(uk.transpose(1, 2), wq_heads[:, :D])                   # Wuk_h^T Wq_h
-            q_rows[:, R: R + P] = wq_heads[:, D:]                                               # the rotated part, as stored
+            q_rows[:, R: R + P] = wq_heads[:, D:][:, turn]                                      # the rotated part
             q_part = q_rows.view(H * row, W).to(dt)
             if self.absorb_values:
                 out_cols = torch.zeros((W, H, row), dtype=f64, device=dev)
@@ -140,7 +148,8 @@ class LatentAttention(Mixer):
             self.w_up_k, self.w_up_v = up_k.contiguous(), up_v.contiguous()
         parts = [q_part]
         if s.has_latent:
-            parts.append(tensors[s.down_name])
+            down = tensors[s.down_name]
+            parts.append(torch.cat([down[:R], down[R:][turn]], dim=0) if P else down)
             if s.latent_norm is not None:
                 self.w_latent_norm = tensors[s.latent_norm_name].contiguous()
             else:

@@ -33,6 +33,7 @@ class Model:
         self.dtype = dtype
         self.blocks: List[Block] = [build_block(b) for b in spec.blocks]
         self.final_norm = build_norm(spec.final_norm)
+        self.embedding_norm = build_norm(spec.embedding_norm) if spec.embedding_norm is not None else None
         self.calls: List[LayerCall] = spec.calls()
         for i, c in enumerate(self.calls):
             if not (0 <= c.layer < len(self.blocks)):
@@ -66,6 +67,9 @@ class Model:
                     out[self._tensor_name(bspec.name + prefix, local)] = info
         for local, info in self.final_norm.parameters().items():
             out[s.final_norm_name + local] = info
+        if self.embedding_norm is not None:
+            for local, info in self.embedding_norm.parameters().items():
+                out[s.embedding_norm_name + local] = info
         if s.head_name is not None:
             out[s.head_name] = ParamInfo((s.vocab_size, s.hidden_size))
         return out
@@ -82,6 +86,8 @@ class Model:
                 part.load({local: tensors[self._tensor_name(full, local)] for local in part.parameters()})
                 part.prepare(self.device, self.dtype)
         self.final_norm.load({local: tensors[s.final_norm_name + local] for local in self.final_norm.parameters()})
+        if self.embedding_norm is not None:
+            self.embedding_norm.load({local: tensors[s.embedding_norm_name + local] for local in self.embedding_norm.parameters()})
 
     def weight_bytes(self) -> int:
         """Bytes of the tensors a decode step reads once (the embedding table only when it
@@ -157,6 +163,10 @@ class Model:
         ops.embedding(h, self.embedding, ctx.token_ids)
         if self.spec.embedding_scale != 1.0:
             ops.scale_cap(h, scale=self.spec.embedding_scale)
+        if self.embedding_norm is not None:
+            if h.dtype != torch.float32 or not hasattr(self.embedding_norm, "triple"):
+                raise RuntimeError("the embedding's norm is a dyt norm on a float32 stream")
+            ops.dyt_step(h, pre=self.embedding_norm.triple(), out=h)        # in place
         ctx.scratch["model_dtype"] = self.dtype
         ctx.scratch.pop("stream_low", None)
         if self.multi_stream():
@@ -445,6 +455,12 @@ class Model:
             n = self.final_norm
             x = torch.empty((row_idx.numel(), h.shape[2]), dtype=self.dtype, device=h.device)
             ops.hyper_step(h, norm_w=n.weight, eps=n.spec.eps, weight_offset=n.spec.weight_offset, out=x, row_idx=row_idx)
+        elif hasattr(pending, "norm") or hasattr(self.final_norm, "triple"):
+            # a last result that passes a norm of its own on its way into the stream, and a dyt final norm: one kernel forms
+            # the wanted rows from stream + norm(result)
+            x = torch.empty((row_idx.numel(), h.shape[1]), dtype=self.dtype, device=h.device)
+            ops.dyt_step(h, branch=pending.y if pending is not None else None, post=pending.norm.triple() if pending is not None else None,
+                         pre=self.final_norm.triple(), out=x, row_idx=row_idx)
         elif h.dtype != self.dtype:
             x = self.final_norm(h, delta=pending, row_idx=row_idx, out_dtype=self.dtype)
         else:

@@ -6,6 +6,10 @@ activation. The experts' matrices are stacked when they are loaded ([experts, 2 
 step routes, groups its (row, choice) pairs by expert on the device, runs the two grouped products and sums a row's
 choices in a fixed order (csrc/moe.cu). Nothing of a step's routing is read on the host.
 
+``routing`` "sigmoid_groups": scores s = sigmoid(z); the choice goes by s + a stored correction, among the experts of the best
+``keep_groups`` of ``groups`` equal groups of neighbours (a group's score: the sum of its two largest choice scores); the
+weights are the chosen experts' s (without the correction) divided by their sum.
+
 ``routing`` "table": there is no router; an integer table [vocab, top] gives every token id its experts (the entries of a
 row differ), each weighted 1 / top. ``shared``: one more expert of the same form that every row uses; its result (float32)
 is added by the kernel that sums a row's choices.
@@ -32,8 +36,12 @@ class RoutedExperts(FeedForward):
         if not 0 < s.top <= s.experts or s.top > 32 or s.intermediate_size <= 0:
             raise ValueError(f"routed_experts: {s.top} of {s.experts} experts (at most 32 a row), ff {s.intermediate_size}")
         ops.glu_code(s.activation)          # refuses a name no kernel knows
-        if s.routing not in ("softmax_top", "table"):
-            raise ValueError(f"routed_experts: routing must be 'softmax_top' or 'table', got {s.routing!r}")
+        if s.routing not in ("softmax_top", "table", "sigmoid_groups"):
+            raise ValueError(f"routed_experts: routing must be 'softmax_top', 'sigmoid_groups' or 'table', got {s.routing!r}")
+        if s.routing == "sigmoid_groups" and (s.groups < 1 or not 1 <= s.keep_groups <= s.groups or s.experts % s.groups
+                                              or (s.experts // s.groups) * s.keep_groups < s.top):
+            raise ValueError(f"routed_experts: {s.experts} experts in {s.groups} groups of which {s.keep_groups} are kept "
+                             f"cannot give {s.top} choices")
         if s.routing == "table" and s.vocab_size <= 0:
             raise ValueError("routed_experts: routing by a table needs the vocabulary's size")
         self.shared = build_feed_forward(s.shared) if s.shared is not None else None
@@ -56,6 +64,8 @@ class RoutedExperts(FeedForward):
             p = {s.table_name: ParamInfo((s.vocab_size, s.top), ("distinct_below", s.experts), integer=True)}
         else:
             p = {s.router_name: ParamInfo((s.experts, W), ("normal", W ** -0.5))}
+            if s.routing == "sigmoid_groups":
+                p[s.correction_name] = ParamInfo((s.experts,), ("normal", 0.1))
         for e in range(s.experts):
             g, u, d = self._names(e)
             p[g] = ParamInfo((F, W), ("normal", W ** -0.5))
@@ -72,6 +82,8 @@ class RoutedExperts(FeedForward):
             self.table = tensors[s.table_name].to(torch.int32).contiguous()
         else:
             self.w_router = tensors[s.router_name].contiguous()
+            if s.routing == "sigmoid_groups":
+                self.correction = tensors[s.correction_name].to(torch.float32).contiguous()
         if self.shared is not None:
             self.shared.load({local: tensors[s.shared_name + local] for local in self.shared.parameters()})
         names = [self._names(e) for e in range(s.experts)]
@@ -84,6 +96,9 @@ class RoutedExperts(FeedForward):
             x = x.contiguous()
         if s.routing == "table":
             routing = ops.moe_route_table(ctx.token_ids, self.table, s.experts)
+        elif s.routing == "sigmoid_groups":
+            routing = ops.moe_route(x, self.w_router, s.top, scoring="sigmoid_groups", correction=self.correction, groups=s.groups,
+                                    keep_groups=s.keep_groups)
         else:
             routing = ops.moe_route(x, self.w_router, s.top)
         add = self.shared.forward(x, ctx, out_dtype=torch.float32) if self.shared is not None else None

@@ -12,7 +12,11 @@ d = beta (v - C^T k), C <- C + k d^T, read-out C^T q, with beta = sigmoid(Wb x) 
 g = exp(-exp(A) softplus(Wa2 Wa1 x + dt)). The read-out is normed per head over vdim with one weight shared by the heads,
 gated by sigmoid(Wg2 Wg1 x), projected out.
 
-Both run as ONE fused input product whose sums stay float32 (gates, decays and everything else that enters the
+"linear_attention" (linear attention with one fixed decay per head, "lightning attention"): q, k and v through silu; per
+head S <- decay_h S + k v^T, read-out S^T q with no other scale; the concatenated heads are RMS-normed together with one
+weight, multiplied by sigmoid(Wg x), projected out.
+
+All run as ONE fused input product whose sums stay float32 (gates, decays and everything else that enters the
 recurrence never pass through the model's type), the scan kernel over the step's rows (prompt portions and single tokens
 alike, csrc/recurrent.cu), the norm-and-gate kernel, and the output product. The state lives in two copies that take
 turns, like the short filter's.
@@ -28,7 +32,7 @@ from ..kernels import ops
 from ..kernels.linear import linear
 from .base import CacheBinding, Mixer
 from .registry import register_mixer
-from .spec import GatedDeltaSpec, MatrixMemorySpec, ParamInfo
+from .spec import GatedDeltaSpec, LinearAttentionSpec, MatrixMemorySpec, ParamInfo
 
 
 def _pad8(n: int) -> int:
@@ -186,4 +190,61 @@ class GatedDelta(Mixer):
                            q_scale=D ** -0.5)
         y = torch.empty((T, H * V), dtype=x.dtype, device=x.device)
         ops.head_norm_gate(y, o, gate, self.norm_w, H, V, s.eps, weight_per_head=False)
+        return linear(y, self.w_o, out_dtype=out_dtype)
+
+
+@register_mixer("linear_attention")
+class LinearAttention(Mixer):
+    graph_safe = True
+    takes_out_dtype = True
+
+    def __init__(self, spec: LinearAttentionSpec) -> None:
+        super().__init__(spec)
+        s = spec
+        if min(s.num_heads, s.qk_dim, s.v_dim) <= 0 or s.qk_dim > 512 or len(s.decays) != s.num_heads:
+            raise ValueError(f"linear_attention: heads {s.num_heads}, dim {s.qk_dim} (at most 512), vdim {s.v_dim}, "
+                             f"{len(s.decays)} decays (one per head)")
+        H, D, V = s.num_heads, s.qk_dim, s.v_dim
+        # columns of the fused product: q | k | v | output gate
+        self.off = {"q": 0, "k": H * D, "v": 2 * H * D, "g": 2 * H * D + H * V}
+        self.cols = 2 * H * D + 2 * H * V
+        self.w_in: Optional[torch.Tensor] = None
+        self.decays: Optional[torch.Tensor] = None
+
+    def parameters(self) -> Dict[str, ParamInfo]:
+        s = self.spec
+        H, D, V, W = s.num_heads, s.qk_dim, s.v_dim, s.hidden_size
+        std = W ** -0.5
+        return {s.q_name: ParamInfo((H * D, W), ("normal", std)), s.k_name: ParamInfo((H * D, W), ("normal", std)),
+                s.v_name: ParamInfo((H * V, W), ("normal", std)), s.gate_name: ParamInfo((H * V, W), ("normal", std)),
+                s.out_name: ParamInfo((W, H * V), ("normal", (H * V) ** -0.5)),
+                s.norm_name: ParamInfo((H * V,), ("one_plus_normal", 0.1))}
+
+    def load(self, tensors: Dict[str, torch.Tensor]) -> None:
+        s = self.spec
+        w = torch.cat([tensors[n] for n in (s.q_name, s.k_name, s.v_name, s.gate_name)], dim=0)
+        pad = _pad8(w.shape[0]) - w.shape[0]
+        if pad:
+            w = torch.cat([w, torch.zeros((pad, w.shape[1]), dtype=w.dtype, device=w.device)], dim=0)
+        self.w_in = w.contiguous()
+        self.w_o = tensors[s.out_name].contiguous()
+        self.norm_w = tensors[s.norm_name].contiguous()
+
+    def prepare(self, device: torch.device, dtype: torch.dtype) -> None:
+        self.decays = torch.tensor([float(d) for d in self.spec.decays], dtype=torch.float64).to(torch.float32).to(device)
+
+    def state_needs(self) -> List[StateNeed]:
+        s = self.spec
+        return [StateNeed((s.num_heads, s.qk_dim * s.v_dim), "float32", phases=2)]
+
+    def forward(self, x: torch.Tensor, ctx, binding: CacheBinding, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        s = self.spec
+        H, D, V = s.num_heads, s.qk_dim, s.v_dim
+        z = linear(x, self.w_in, out_dtype=torch.float32)
+        o = torch.empty((x.shape[0], H * V), dtype=torch.float32, device=x.device)
+        ops.recurrent_scan(ops.SCAN_LINEAR_DECAY, o, z, (self.off["q"], self.off["k"], self.off["v"]), z, (0, 0),
+                           ctx.cache.state_tensor(binding.states[0]), ctx, H, H, D, V, p0=self.decays)
+        y = torch.empty((x.shape[0], H * V), dtype=x.dtype, device=x.device)
+        # the norm runs over all heads together: one "head" of H * V numbers
+        ops.head_norm_gate(y, o, z[:, self.off["g"]: self.off["g"] + H * V], self.norm_w, 1, H * V, s.eps, weight_per_head=True)
         return linear(y, self.w_o, out_dtype=out_dtype)

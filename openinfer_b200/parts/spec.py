@@ -34,6 +34,10 @@ class NormSpec:
     eps: float = 1e-6
     weight_offset: float = 0.0  # scale is (weight_offset + w)
     param_name: str = "weight"  # local tensor name (appended to the prefix the enclosing part gives the norm)
+    # kind "dyt" (Dynamic Tanh: tanh(alpha x) w + b, no mean and no variance; eps is not used): the bias vector and the
+    # scalar alpha are stored beside the weight under its name + these suffixes
+    bias_suffix: str = ".b"
+    alpha_suffix: str = ".alpha"
 
 
 @dataclasses.dataclass(frozen=True)
@@ -92,6 +96,14 @@ class AttentionSpec:
     sink_name: str = "sink"
     head_gate: bool = False                 # head h's output is multiplied by sigmoid(W_g x)_h (``gate_name`` [heads, hidden])
     gate_name: str = "g"
+    qkv_bias: bool = False                  # q, k and v have biases (tensor name + ``bias_suffix``), added in the projection
+    bias_suffix: str = ".b"
+    # > 0: AFTER the rotation q and k heads are divided by their root mean square over qk_dim numbers (no weight), with
+    # this eps inside the root; takes the place of ``qk_norm``, which norms before the rotation
+    unit_norm_after_rotation_eps: float = 0.0
+    # with a window: the first ``keep_first`` keys of a sequence stay visible to every later query (at their true
+    # positions), and their pages are never given back
+    keep_first: int = 0
 
 
 @dataclasses.dataclass(frozen=True)
@@ -227,8 +239,14 @@ class RoutedExpertsSpec:
     up_name: str = "up"
     down_name: str = "down"
     # "softmax_top": the ``top`` largest router logits, weighted by their softmax. "table": no router; an integer tensor
-    # ``table_name`` [vocab_size, top] gives every token id its experts, each weighted 1 / top
+    # ``table_name`` [vocab_size, top] gives every token id its experts, each weighted 1 / top. "sigmoid_groups": scores
+    # s = sigmoid(logit); the choice goes by s + a stored correction (``correction_name`` [experts]) among the experts of
+    # the ``keep_groups`` best of ``groups`` equal groups of neighbours (a group's score: the sum of its two largest choice
+    # scores); the weights are the chosen experts' s divided by their sum
     routing: str = "softmax_top"
+    correction_name: str = "correction"
+    groups: int = 1
+    keep_groups: int = 1
     table_name: str = "table"
     vocab_size: int = 0
     # an expert of the same form that every row uses, added to the routed sum (a GatedMlpSpec; tensors under ``shared_name``)
@@ -266,6 +284,27 @@ class GatedDeltaSpec:
     eps: float = 1e-6
     decay_rank: int = 0                     # what random weights use; a checkpoint's own sizes win
     gate_rank: int = 0
+
+
+@dataclasses.dataclass(frozen=True)
+class LinearAttentionSpec:
+    """Linear attention with one fixed decay per head ("lightning attention"): q, k (``qk_dim``) and v (``v_dim``) through
+    silu; per head S <- decay_h S + k v^T, read-out S^T q with no other scale; the concatenated heads are RMS-normed together
+    (weight ``norm_name`` [heads * v_dim]), multiplied by sigmoid(W_g x) and projected out. S is float32 state per request."""
+
+    kind: str = "linear_attention"
+    hidden_size: int = 0
+    num_heads: int = 0
+    qk_dim: int = 0
+    v_dim: int = 0
+    decays: Tuple[float, ...] = ()          # one per head
+    eps: float = 1e-6
+    q_name: str = "q"
+    k_name: str = "k"
+    v_name: str = "v"
+    gate_name: str = "g"
+    out_name: str = "o"
+    norm_name: str = "norm"
 
 
 @dataclasses.dataclass(frozen=True)
@@ -307,6 +346,12 @@ class BlockSpec:
     feed_forward_streams_name: str = "hc2."
     token_input: Any = None                      # blocks that end with a per-token input (TokenInputSpec)
     token_input_name: str = "side."
+    # blocks that also norm their sublayers' OUTPUTS ("sandwich": x <- x + out_norm(f(in_norm(x)))): ``input_norm`` and
+    # ``post_norm`` are the norms of the two inputs, these the norms of the two results
+    mixer_out_norm: Optional[NormSpec] = None
+    feed_forward_out_norm: Optional[NormSpec] = None
+    mixer_out_norm_name: str = "norm1b"
+    feed_forward_out_norm_name: str = "norm2b"
 
 
 @dataclasses.dataclass(frozen=True)
@@ -338,6 +383,8 @@ class ModelSpec:
     logit_scale: float = 1.0         # the logits are multiplied by this
     residual_dtype: str = "model"    # "model": the stream between layers has the model's type; "float32": always 32-bit
     streams: int = 1                 # residual streams a row travels as ([tokens, streams, hidden]; blocks of kind "hyper")
+    embedding_norm: Optional[NormSpec] = None     # a norm applied to the embedded rows before the first block
+    embedding_norm_name: str = "embed.norm"
 
     def calls(self) -> List[LayerCall]:
         return [c if isinstance(c, LayerCall) else LayerCall(int(c)) for c in self.order]
