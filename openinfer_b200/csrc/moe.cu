@@ -101,9 +101,11 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
       for (int kept = 0; kept < keep_groups; ++kept) {
         float best = -INFINITY;
         int bg = 0x7fffffff;
+        // (a group is kept already when its experts are open; the first open candidate stands whatever its score is, so
+        // that rows of a padded step, whose numbers mean nothing and may be NaN, still name experts that exist)
         for (int g = lane; g < n_groups; g += 32) {
           const float v = gs[g];
-          if (v > -INFINITY && (bg == 0x7fffffff || v > best)) { best = v; bg = g; }
+          if (taken[g * per] && (bg == 0x7fffffff || v > best)) { best = v; bg = g; }
         }
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
@@ -113,7 +115,6 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
         }
         if (bg == 0x7fffffff) break;
         for (int i = lane; i < per; i += 32) taken[bg * per + i] = 0;
-        if (lane == 0) gs[bg] = -INFINITY;
         __syncwarp();
       }
     }
@@ -140,6 +141,7 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
         be = oe;
       }
     }
+    if (be >= E) be = j;          // nothing open (cannot happen with sizes the entry point accepts): still an expert that exists
     if (lane == 0) taken[be] = 1;
     __syncwarp();
     chosen_z[j] = best;
