@@ -82,7 +82,8 @@ def build_spec(cfg: LuzitarConfig) -> ModelSpec:
         vocab_size=cfg.vocab, hidden_size=W, blocks=tuple(blocks), order=tuple(order), final_norm=norm, embedding_name="embed",
         final_norm_name="final.norm", head_name="head", max_positions=cfg.max_position_embeddings,
         stop_token_ids=tuple(cfg.stop_token_ids), logit_soft_cap=float(cfg.logit_softcap), residual_dtype="float32",
-        embedding_norm=norm, embedding_norm_name="embed.norm")
+        embedding_norm=norm, embedding_norm_name="embed.norm",
+        embedding_init=("normal", 1.0))      # random weights: rows that the norm behind the table tells apart
 
 
 register_architecture(LuzitarConfig.architecture, LuzitarConfig, build_spec)

@@ -60,7 +60,7 @@ class Model:
 
     def expected_tensors(self) -> Dict[str, ParamInfo]:
         s = self.spec
-        out: Dict[str, ParamInfo] = {s.embedding_name: ParamInfo((s.vocab_size, s.hidden_size))}
+        out: Dict[str, ParamInfo] = {s.embedding_name: ParamInfo((s.vocab_size, s.hidden_size), s.embedding_init)}
         for block, bspec in zip(self.blocks, s.blocks):
             for prefix, part in block.sub_parts().items():
                 for local, info in part.parameters().items():

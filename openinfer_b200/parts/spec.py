@@ -384,6 +384,7 @@ class ModelSpec:
     residual_dtype: str = "model"    # "model": the stream between layers has the model's type; "float32": always 32-bit
     streams: int = 1                 # residual streams a row travels as ([tokens, streams, hidden]; blocks of kind "hyper")
     embedding_norm: Optional[NormSpec] = None     # a norm applied to the embedded rows before the first block
+    embedding_init: Tuple = ("normal", 0.02)      # how random weights draw the embedding table
     embedding_norm_name: str = "embed.norm"
 
     def calls(self) -> List[LayerCall]:

@@ -155,11 +155,14 @@ def latent_attention(h, p, pre, m: dict, eps: float, cached):
     return out.reshape(T, H * V) @ p[pre + "o"].T
 
 
-def route(h, p, pre, router: dict):
-    """Chosen experts [T, top] and their weights."""
+def route(h, p, pre, router: dict, margins: Optional[list] = None):
+    """Chosen experts [T, top] and their weights. ``margins`` collects, per row, how far the choice is from another one:
+    the gap between the last chosen and the first unchosen choice score, and between the last kept and the first dropped
+    group."""
     E, top = int(router["experts"]), int(router["top"])
     s = torch.sigmoid(h.to(torch.float64) @ p[pre + "router"].to(torch.float64).T)
     choice = s + p[pre + "correction"].to(torch.float64)
+    margin = torch.full((h.shape[0],), float("inf"), dtype=torch.float64)
     groups = router.get("groups")
     if groups:
         n, keep = int(groups["count"]), int(groups["keep"])
@@ -167,10 +170,19 @@ def route(h, p, pre, router: dict):
         by_group = choice.view(-1, n, per)
         score = by_group.topk(min(2, per), dim=-1).values.sum(dim=-1)
         best = score.topk(keep, dim=-1).indices
+        if keep < n:
+            ranked = score.sort(dim=-1, descending=True).values
+            margin = torch.minimum(margin, ranked[:, keep - 1] - ranked[:, keep])
         allowed = torch.zeros((h.shape[0], n), dtype=torch.bool)
         allowed.scatter_(1, best, True)
         choice = choice.masked_fill(~allowed[:, :, None].expand(-1, -1, per).reshape(-1, E), float("-inf"))
     ids = choice.topk(top, dim=-1).indices
+    ranked = choice.sort(dim=-1, descending=True).values
+    if top < E:
+        gap = ranked[:, top - 1] - ranked[:, top]
+        margin = torch.minimum(margin, torch.where(torch.isfinite(ranked[:, top]), gap, torch.full_like(gap, float("inf"))))
+    if margins is not None:
+        margins.append(margin)
     w = s.gather(1, ids)
     w = w / (w.sum(dim=-1, keepdim=True) + 1e-20)
     return ids, w.to(h.dtype)
@@ -182,8 +194,8 @@ def expert(h, p, pre, limit: float):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ p[pre + "down"].T
 
 
-def experts(h, p, pre, mlp: dict):
-    ids, w = route(h, p, pre, mlp["router"])
+def experts(h, p, pre, mlp: dict, margins: Optional[list] = None):
+    ids, w = route(h, p, pre, mlp["router"], margins)
     out = torch.zeros_like(h)
     limit = float(mlp["expert"]["limit"])
     for t in range(h.shape[0]):
@@ -192,15 +204,23 @@ def experts(h, p, pre, mlp: dict):
     return out
 
 
-def forward(cfg: dict, p: Dict[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None):
-    """Logits [T, vocab] of one sequence; ``layers_out`` collects the stream after every layer."""
+def forward(cfg: dict, p: Dict[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None, dtype=torch.float64,
+            round_to=None, margins: Optional[list] = None):
+    """Logits [T, vocab] of one sequence in ``dtype``; ``layers_out`` collects the stream after every layer. ``round_to``:
+    the sublayers' normed inputs are rounded to this type on the way (what a 16-bit engine does at least). ``margins``
+    collects every routed layer's per-row distance from another choice."""
+    p = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in p.items()}
     eps = float(cfg["norm"]["eps"])
+
+    def dyt_in(x, name):
+        h = dyt(x, p, name)
+        return h.to(round_to).to(dtype) if round_to is not None else h
     x = dyt(p["embed"][torch.tensor(tokens)], p, "embed.norm")
     cached = {}
     for i, layer in enumerate(cfg["layers"]):
         pre = f"l{i}."
         m = layer["mixer"]
-        h = dyt(x, p, pre + "norm1")
+        h = dyt_in(x, pre + "norm1")
         if layer["type"] == "lightning":
             a = lightning(h, p, pre + "mix.", m, eps)
         elif layer["type"] == "attention":
@@ -216,11 +236,11 @@ def forward(cfg: dict, p: Dict[str, torch.Tensor], tokens: List[int], layers_out
             raise ValueError(layer["type"])
         x = x + dyt(a, p, pre + "norm1b")
         if layer.get("mlp"):
-            h = dyt(x, p, pre + "norm2")
-            x = x + dyt(experts(h, p, pre + "mlp.", layer["mlp"]), p, pre + "norm2b")
+            h = dyt_in(x, pre + "norm2")
+            x = x + dyt(experts(h, p, pre + "mlp.", layer["mlp"], margins), p, pre + "norm2b")
         if layers_out is not None:
             layers_out.append(x.clone())
-    x = dyt(x, p, "final.norm")
+    x = dyt_in(x, "final.norm")
     logits = x @ p["head"].T
     cap = float(cfg.get("logit_softcap") or 0.0)
     return cap * torch.tanh(logits / cap) if cap > 0 else logits
