@@ -153,8 +153,13 @@ attention_mma_kernel(const AttnParams p) {
   if (p.window > 0) lo = max(0, pos0 - p.window + 1);
   const int hi = pos0 + tile_toks;                        // exclusive: last token's own key included
   lo &= ~(kKeys - 1);
-  // this item's slice of [lo, hi), in whole tiles
-  const int span_tiles = (hi - lo + kKeys - 1) / kKeys;
+  // a window that keeps the sequence's first keys visible: the tiles that hold them come first in the item's list of
+  // tiles, as far as they lie wholly in front of the window's tiles (the others are among those anyway)
+  const int keep_first = (MODS && p.window > 0) ? p.mods.keep_first : 0;
+  const int kept_tiles = keep_first > 0 ? min((keep_first + kKeys - 1) / kKeys, lo / kKeys) : 0;
+  auto tile_key = [&](int t) { return t < kept_tiles ? t * kKeys : lo + (t - kept_tiles) * kKeys; };
+  // this item's slice of the kept tiles and [lo, hi), in whole tiles
+  const int span_tiles = kept_tiles + (hi - lo + kKeys - 1) / kKeys;
   const int tiles_per_split = (span_tiles + nsplits - 1) / nsplits;
   const int t_begin = split * tiles_per_split;
   const int t_end = min(span_tiles, t_begin + tiles_per_split);
@@ -234,23 +239,23 @@ attention_mma_kernel(const AttnParams p) {
 
   int page_next = -1;      // page of this thread's row in the tile after the one being loaded
   if (t_begin < t_end) {
-    const int page0 = tile_page(p, bt, lo + t_begin * kKeys, hi);
-    page_next = t_begin + 1 < t_end ? tile_page(p, bt, lo + (t_begin + 1) * kKeys, hi) : -1;
-    load_tile<HD>(k_tile(0), p.k_cache, p, page0, kvh, lo + t_begin * kKeys);
+    const int page0 = tile_page(p, bt, tile_key(t_begin), hi);
+    page_next = t_begin + 1 < t_end ? tile_page(p, bt, tile_key(t_begin + 1), hi) : -1;
+    load_tile<HD>(k_tile(0), p.k_cache, p, page0, kvh, tile_key(t_begin));
     cp_async_commit();
-    load_tile<HD>(v_tile(0), p.v_cache, p, page0, kvh, lo + t_begin * kKeys);
+    load_tile<HD>(v_tile(0), p.v_cache, p, page0, kvh, tile_key(t_begin));
     cp_async_commit();
   }
   for (int t = t_begin; t < t_end; ++t) {
     const int buf = (t - t_begin) & 1;
-    const int key0 = lo + t * kKeys;
+    const int key0 = tile_key(t);
     const bool more = t + 1 < t_end;
     if (more) {
       const int page = page_next;
-      page_next = t + 2 < t_end ? tile_page(p, bt, key0 + 2 * kKeys, hi) : -1;   // used next iteration
-      load_tile<HD>(k_tile(buf ^ 1), p.k_cache, p, page, kvh, key0 + kKeys);
+      page_next = t + 2 < t_end ? tile_page(p, bt, tile_key(t + 2), hi) : -1;   // used next iteration
+      load_tile<HD>(k_tile(buf ^ 1), p.k_cache, p, page, kvh, tile_key(t + 1));
       cp_async_commit();
-      load_tile<HD>(v_tile(buf ^ 1), p.v_cache, p, page, kvh, key0 + kKeys);
+      load_tile<HD>(v_tile(buf ^ 1), p.v_cache, p, page, kvh, tile_key(t + 1));
       cp_async_commit();
       cp_async_wait<3>();   // Q and K of this tile have landed
     } else {
@@ -295,7 +300,8 @@ attention_mma_kernel(const AttnParams p) {
         }
       }
       // ---- mask (only where a row may not see the whole tile) + online softmax
-      const bool full = key0 + kKeys - 1 <= warp_first_pos && (p.window <= 0 || key0 > warp_last_pos - p.window) &&
+      const bool full = key0 + kKeys - 1 <= warp_first_pos &&
+                        (p.window <= 0 || key0 > warp_last_pos - p.window || key0 + kKeys <= keep_first) &&
                         warp_row0 + 16 * MT <= tile_toks * group;
       if (MODS) {
 #pragma unroll
@@ -325,7 +331,8 @@ attention_mma_kernel(const AttnParams p) {
             for (int e = 0; e < 4; ++e) {
               const int i = e >> 1;
               const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
-              const bool ok = row_ok[mt][i] && key <= pos[mt][i] && (p.window <= 0 || key > pos[mt][i] - p.window);
+              const bool ok = row_ok[mt][i] && key <= pos[mt][i] &&
+                              (p.window <= 0 || key > pos[mt][i] - p.window || key < keep_first);
               s[mt][j][e] = ok ? s[mt][j][e] : -INFINITY;
               m_new[i] = fmaxf(m_new[i], s[mt][j][e]);
             }
@@ -578,7 +585,12 @@ attention_decode_kernel(const AttnParams p) {
   const int pos = kv_len - 1;
   int lo = 0;
   if (p.window > 0) lo = max(0, pos - p.window + 1) & ~(kDecKeys - 1);
-  const int span_tiles = (kv_len - lo + kDecKeys - 1) / kDecKeys;
+  // a window that keeps the sequence's first keys visible: their tiles come first in the row's list of tiles, as far as
+  // they lie wholly in front of the window's
+  const int keep_first = (MODS && p.window > 0) ? p.mods.keep_first : 0;
+  const int kept_tiles = keep_first > 0 ? min((keep_first + kDecKeys - 1) / kDecKeys, lo / kDecKeys) : 0;
+  auto tile_key = [&](int t) { return t < kept_tiles ? t * kDecKeys : lo + (t - kept_tiles) * kDecKeys; };
+  const int span_tiles = kept_tiles + (kv_len - lo + kDecKeys - 1) / kDecKeys;
   const int tiles_per_split = (span_tiles + nsplits - 1) / nsplits;
   const int t_begin = min(span_tiles, split * tiles_per_split);
   const int t_end = min(span_tiles, t_begin + tiles_per_split);
@@ -618,15 +630,20 @@ attention_decode_kernel(const AttnParams p) {
   // the next tile to copy: its first key, its page (index into the block table) and offset there
   const long long v_delta = p.v_cache - p.k_cache;
   int ld_t = t_begin, ld_stage = 0;
-  int ld_key = lo + t_begin * kDecKeys;
+  int ld_key = tile_key(t_begin);
   int ld_pg = ld_key / p.page_size, ld_off = ld_key % p.page_size;
   auto issue_next = [&]() {   // one commit per call, empty when past the end
     if (ld_t < t_end) {
       load_kv_tile16<HD>(k_tile(ld_stage), v_tile(ld_stage), p, bt, v_delta, kvh, ld_key, kv_len, tl, aligned, ld_pg, ld_off);
       ++ld_t;
-      ld_key += kDecKeys;
-      ld_off += kDecKeys;
-      if (ld_off >= p.page_size) { ld_off -= p.page_size; ++ld_pg; }   // aligned case: exact
+      if (ld_t == kept_tiles) {        // behind the kept tiles the window's begin
+        ld_key = lo;
+        ld_pg = lo / p.page_size, ld_off = lo % p.page_size;
+      } else {
+        ld_key += kDecKeys;
+        ld_off += kDecKeys;
+        if (ld_off >= p.page_size) { ld_off -= p.page_size; ++ld_pg; }   // aligned case: exact
+      }
       ld_stage = ld_stage + 1 == kDecStages ? 0 : ld_stage + 1;
     }
     cp_async_commit();
@@ -730,7 +747,7 @@ attention_decode_kernel(const AttnParams p) {
     for (int t = t_begin; t < t_end; ++t) {
       cp_async_wait<kDecStages - 1>();   // tile t (this thread's part) has landed ...
       __syncwarp();                      // ... and so have the other lanes' parts
-      const int key0 = lo + t * kDecKeys;
+      const int key0 = tile_key(t);
       if (insert && t == span_tiles - 1) {
         // what the copy brought for the step's own row is whatever the page held: the new key and value replace it
         const int r = pos - key0;
@@ -756,7 +773,7 @@ attention_decode_kernel(const AttnParams p) {
       float m_new[2] = {m[0], m[1]};
       // a tile whose every key every row sees needs no mask (rows beyond the group hold zeros
       // and are never stored)
-      const bool full = key0 + kDecKeys <= kv_len && (p.window <= 0 || key0 > pos - p.window);
+      const bool full = key0 + kDecKeys <= kv_len && (p.window <= 0 || key0 > pos - p.window || key0 + kDecKeys <= keep_first);
       const float sl2 = MODS ? 1.f : p.scale_log2;
       if (MODS) {
 #pragma unroll
@@ -781,7 +798,7 @@ attention_decode_kernel(const AttnParams p) {
           for (int e = 0; e < 4; ++e) {
             const int i = e >> 1;
             const int key = key0 + j * 8 + (lane & 3) * 2 + (e & 1);
-            const bool ok = key <= pos && (p.window <= 0 || key > pos - p.window);
+            const bool ok = key <= pos && (p.window <= 0 || key > pos - p.window || key < keep_first);
             s[j][e] = ok ? s[j][e] * sl2 : -INFINITY;
             m_new[i] = fmaxf(m_new[i], s[j][e]);
           }

@@ -340,7 +340,7 @@ def tcgen05_status() -> int:
 
 
 FUSE_ROPE_IN_DECODE = True
-KEPT_KEYS_ON_TENSOR_CORES = False   # windows that keep a sequence's first keys visible: the general kernel
+KEPT_KEYS_ON_TENSOR_CORES = True    # windows that keep a sequence's first keys visible run on the mma.sync tile and decode kernels (False: the general kernel)
 MODS_ON_TENSOR_CORES = True    # layers that modify their scores run on the mma.sync tile and decode kernels (False: the general kernel)
 
 

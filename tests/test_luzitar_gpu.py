@@ -454,7 +454,7 @@ def sharpen(path, layer=0, kinds=("q", "k", "v"), by=6.0, out_by=8.0):
 def _sharp_attention_model(tmp_path, window, keep, name, heads=(2, 1), dim=16, page_conv=2):
     """One attention layer whose key 'keep - 1' (the last kept one), key 'keep' (the first not kept) and the keys at the
     window's edge decide rows far behind them: the queries are lengthened so that the softmax is sharp."""
-    cfg = _one_layer(attn(heads[0], heads[1], dim, 16, 4.0 / math.sqrt(dim), window=window, keep_first=keep, conv=page_conv, rot=rot(4, 50.0)))
+    cfg = _one_layer(attn(heads[0], heads[1], dim, min(dim, 32), 4.0 / math.sqrt(dim), window=window, keep_first=keep, conv=page_conv, rot=rot(4, 50.0)))
     path = make_folder(str(tmp_path / name), cfg, window * 7 + keep)
     sharpen(path)
     return cfg, path
@@ -486,15 +486,16 @@ def test_windows_and_kept_keys_at_and_around_page_borders(tmp_path):
     """Windows of 15, 16, 17, 32 and 33 keys and 15, 16, 17, 1 and 40 kept keys with pages of 16: the oldest key seen and the
     last kept one are the last of a page, the first of one, and one to either side; prompts and decoded tokens, portions
     that end inside a page; pages behind the window are given back on the way, the kept ones are not."""
-    for window, keep in ((15, 16), (16, 17), (17, 15), (32, 1), (33, 40)):
-        cfg, path = _sharp_attention_model(tmp_path, window, keep, f"w{window}")
-        toks = tokens_for(cfg, 130, window)
+    for window, keep, dim in ((15, 16, 16), (16, 17, 32), (17, 15, 32), (32, 1, 16), (33, 40, 64), (70, 65, 32)):
+        # (heads of 32 and 64 numbers: the tensor-core kernels in bfloat16, whose tiles hold 64 and 16 keys)
+        cfg, path = _sharp_attention_model(tmp_path, window, keep, f"w{window}", dim=dim)
+        toks = tokens_for(cfg, 190, window)
         for dtype in DTYPES:
-            runner = runner_for(path, dtype, max_tokens=192)
-            steps = trace_portions({"w": toks[:90]}, sizes=(13, 16, 3, 17, 21))
+            runner = runner_for(path, dtype, max_tokens=256)
+            steps = trace_portions({"w": toks[:150]}, sizes=(13, 16, 3, 17, 21, 70))
             steps[-1]["end"] = []
             steps += [{"step": 100 + i, "entries": [{"id": "w", "tokens": [t], "want": [0]}], "end": ["w"] if i == 39 else []}
-                      for i, t in enumerate(toks[90:])]
+                      for i, t in enumerate(toks[150:])]
             got = replay_in_process(runner, steps)["w"]
             compare(got, path, toks, dtype, f"window {window} keep {keep} {dtype}")
         raw, tensors = read_folder(path)
