@@ -23,7 +23,10 @@ real models beside Qwen3 at equal sizes (decode at batch 1 / 8 / 64, a 2,048-tok
 every kernel's time per step), one JSON line of its own. ``--design pilonex`` does the same for the Pilonex design
 (hyper-connection streams, windowed attention beside a gated delta rule, matrix memories, dense and routed feed-forwards),
 ``--design bubalix`` for the Bubalix design (filtered, capped, windowed attention with sinks and latent attention with a
-rotated key part under one norm with experts picked by a token table, a shared expert and a side input per token).
+rotated key part under one norm with experts picked by a token table, a shared expert and a side input per token),
+``--design luzitar`` for the Luzitar design (Dynamic Tanh norms on both sides of every sublayer, linear attention with a
+fixed decay per head, attention normed behind its rotation under a window that keeps the first keys, latent attention whose
+cache a later layer reads, experts chosen by corrected sigmoid scores within the best groups).
 """
 from __future__ import annotations
 
@@ -484,6 +487,33 @@ def bubalix_configs(key, layers=None):
     return bubalix, design_configs(key, layers)[1]
 
 
+def luzitar_configs(key, layers=None):
+    """Luzitar at the same widths and depths: of every four layers one is "lightning" (linear attention with a fixed decay per
+    head, half as many heads of 128 keys and 128 values), one "attention" (grouped-query with per head 128 keys and values, a
+    quarter as many kv heads, biases, four-tap filters on q, k and v, half of each head rotated with stretched waves, the
+    unit norm behind the rotation, a window that keeps the first 64 keys) and two "latent_attention" (a latent of 96 numbers
+    and a rotated key part of 32 in one cached row of 128; the second reads the first one's cache); every layer has sixteen
+    experts of a quarter of Qwen3's feed-forward in four groups of which the two best are open, two experts a token. Qwen3 as
+    in ``design_configs``."""
+    width, n_layers, heads, window, _, inter = DESIGN_SIZES[key]
+    n_layers = layers or n_layers
+    lin_heads = max(1, heads // 2)
+    lin = {"heads": lin_heads, "dim": 128, "vdim": 128, "decay": [1.0 - 2.0 ** -(3 + 6 * h / max(1, lin_heads - 1)) for h in range(lin_heads)]}
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 0.2, "mask": {"size": window, "keep_first": 64},
+           "conv": 4, "rot": {"dims": 64, "base": 500000.0, "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    lat = {"heads": heads, "dim": 128, "rot_dim": 32, "vdim": 128, "kv_rank": 96, "scale": 160 ** -0.5, "rot": {"dims": 32, "base": 500000.0}}
+    mlp = {"kind": "moe", "expert": {"ff": inter // 4, "limit": 7.0}, "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    lay = []
+    for i in range(n_layers):
+        kind = ("lightning", "attention", "latent_attention", "latent_attention")[i % 4]
+        m = dict({"lightning": lin, "attention": att, "latent_attention": lat}[kind])
+        if i % 4 == 3:
+            m["kv_from"] = i - 1
+        lay.append({"type": kind, "mixer": m, "mlp": dict(mlp)})
+    luzitar = {"architecture": "Luzitar", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": lay}
+    return luzitar, design_configs(key, layers)[1]
+
+
 def _part_tensors(torch, part, seen=None):
     """Every tensor a part holds, the tensors of parts inside it included."""
     seen = set() if seen is None else seen
@@ -626,7 +656,7 @@ class DesignBench:
                 flops += 4.0 * heads * row * seen
             for m in (block.mixer, getattr(block.mixer, "left", None), getattr(block.mixer, "right", None)):
                 sp = getattr(m, "spec", None)
-                if sp is not None and getattr(sp, "kind", "") in ("matrix_memory", "gated_delta"):   # memory update and read-out
+                if sp is not None and getattr(sp, "kind", "") in ("matrix_memory", "gated_delta", "linear_attention"):   # memory update and read-out
                     flops += 6.0 * T * sp.num_heads * sp.qk_dim * sp.v_dim
         return flops + 2.0 * self.vocab * model.spec.hidden_size
 
@@ -662,7 +692,7 @@ def design_mode(args, torch, mods, peaks, peaks_src):
             if key not in DESIGN_SIZES:
                 raise SystemExit(f"--design-sizes: unknown size {key!r} (known: {', '.join(DESIGN_SIZES)})")
             rec = {"width": DESIGN_SIZES[key][0], "layers": args.layers or DESIGN_SIZES[key][1]}
-            configs = {"pilonex": pilonex_configs, "bubalix": bubalix_configs}.get(args.design, design_configs)(key, args.layers)
+            configs = {"pilonex": pilonex_configs, "bubalix": bubalix_configs, "luzitar": luzitar_configs}.get(args.design, design_configs)(key, args.layers)
             for arch, cfg in zip((args.design, "qwen3"), configs):
                 b = DesignBench(torch, mods, cfg, args.dtype, CONTEXT, 64, steps + warm + 16)
                 r = {"weights_gb": round(b.runner.model.weight_bytes() / 1e9, 3)}
@@ -723,7 +753,7 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill", "mixed", "sampler"], default=None,
                     help="run warm-up, then ONE step between cudaProfilerStart/Stop and exit "
                          "(for `ncu --profile-from-start off`); prints no benchmark line")
-    ap.add_argument("--design", default=None, choices=["delunex", "pilonex", "bubalix"],
+    ap.add_argument("--design", default=None, choices=["delunex", "pilonex", "bubalix", "luzitar"],
                     help="instead of the headline workload: this design at layer sizes of real models beside Qwen3 at equal "
                          "sizes (decode at batch 1/8/64, a 2,048-token prefill), one JSON line")
     ap.add_argument("--design-sizes", default=None, help="sizes for --design, comma separated (1k, 2k, 4k; default 1k,2k)")

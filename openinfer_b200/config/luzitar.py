@@ -73,6 +73,8 @@ class LuzitarConfig(ModelConfig):
                 _positive_int(mw, m, key)
             if layer["type"] == "lightning":
                 decay = m.get("decay")
+                if isinstance(decay, (int, float)) and not isinstance(decay, bool):
+                    decay = [decay] * heads                  # one number for all heads
                 if not isinstance(decay, (list, tuple)) or len(decay) != heads or any(
                         isinstance(d, bool) or not isinstance(d, (int, float)) or not 0.0 <= d <= 1.0 for d in decay):
                     raise ConfigError(f"{mw}: 'decay' must list one number in [0, 1] per head ({heads})")

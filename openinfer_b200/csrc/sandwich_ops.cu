@@ -31,7 +31,28 @@ struct DytParams {
   int dtype;
 };
 
-template <typename TO>
+// four neighbouring numbers of a parameter vector (index a multiple of four), 8 or 16 bytes at a time
+__device__ __forceinline__ void load4_as_f32(const void* p, int dtype, int i, float (&out)[4]) {
+  if (dtype == OI_F32) {
+    const float4 t = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(p) + i);
+    out[0] = t.x, out[1] = t.y, out[2] = t.z, out[3] = t.w;
+  } else {
+    const uint2 t = *reinterpret_cast<const uint2*>(reinterpret_cast<const bf16*>(p) + i);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+    out[0] = a.x, out[1] = a.y, out[2] = b.x, out[3] = b.y;
+  }
+}
+__device__ __forceinline__ void store4(float* o, const float (&v)[4]) { *reinterpret_cast<float4*>(o) = make_float4(v[0], v[1], v[2], v[3]); }
+__device__ __forceinline__ void store4(bf16* o, const float (&v)[4]) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v[0], v[1]), b = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 t;
+  t.x = *reinterpret_cast<unsigned*>(&a), t.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(o) = t;
+}
+
+// kVec: the width is a multiple of four and every pointer 16-byte aligned: four numbers a thread, 8- and 16-byte accesses
+template <typename TO, bool kVec>
 __global__ void dyt_step_kernel(float* __restrict__ h, const float* __restrict__ branch, DytParams post, DytParams pre,
                                 TO* __restrict__ out, const int* __restrict__ row_idx, int width) {
   pdl_start();
@@ -42,8 +63,7 @@ __global__ void dyt_step_kernel(float* __restrict__ h, const float* __restrict__
   const float a_pre = out ? load_as_f32(pre.alpha, pre.dtype, 0) : 0.f;
   for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 4; c < width; c += gridDim.y * blockDim.x * 4) {
     float v[4];
-    const bool vec = c + 4 <= width && (width & 3) == 0;
-    if (vec) {
+    if (kVec) {
       const float4 t = *reinterpret_cast<const float4*>(hr + c);
       v[0] = t.x, v[1] = t.y, v[2] = t.z, v[3] = t.w;
     } else {
@@ -52,26 +72,39 @@ __global__ void dyt_step_kernel(float* __restrict__ h, const float* __restrict__
     }
     if (branch) {
       const float* br = branch + (size_t)row * width;
+      if (kVec) {
+        const float4 t = *reinterpret_cast<const float4*>(br + c);
+        const float y[4] = {t.x, t.y, t.z, t.w};
+        float w[4], b[4];
+        load4_as_f32(post.w, post.dtype, c, w);
+        load4_as_f32(post.b, post.dtype, c, b);
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (c + e < width)
-          v[e] += tanhf(a_post * br[c + e]) * load_as_f32(post.w, post.dtype, c + e) + load_as_f32(post.b, post.dtype, c + e);
-      if (row_idx) {
-        // gathered rows: the stream is not read again, the sum stays in registers
-      } else if (vec) {
-        *reinterpret_cast<float4*>(hr + c) = make_float4(v[0], v[1], v[2], v[3]);
+        for (int e = 0; e < 4; ++e) v[e] += tanhf(a_post * y[e]) * w[e] + b[e];
+        if (!row_idx) store4(hr + c, v);        // gathered rows: the stream is not read again, the sum stays in registers
       } else {
 #pragma unroll
         for (int e = 0; e < 4; ++e)
-          if (c + e < width) hr[c + e] = v[e];
+          if (c + e < width) {
+            v[e] += tanhf(a_post * br[c + e]) * load_as_f32(post.w, post.dtype, c + e) + load_as_f32(post.b, post.dtype, c + e);
+            if (!row_idx) hr[c + e] = v[e];
+          }
       }
     }
     if (out) {
       TO* o = out + (size_t)r * width;
+      if (kVec) {
+        float w[4], b[4], y[4];
+        load4_as_f32(pre.w, pre.dtype, c, w);
+        load4_as_f32(pre.b, pre.dtype, c, b);
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (c + e < width)
-          o[c + e] = from_f32<TO>(tanhf(a_pre * v[e]) * load_as_f32(pre.w, pre.dtype, c + e) + load_as_f32(pre.b, pre.dtype, c + e));
+        for (int e = 0; e < 4; ++e) y[e] = tanhf(a_pre * v[e]) * w[e] + b[e];
+        store4(o + c, y);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (c + e < width)
+            o[c + e] = from_f32<TO>(tanhf(a_pre * v[e]) * load_as_f32(pre.w, pre.dtype, c + e) + load_as_f32(pre.b, pre.dtype, c + e));
+      }
     }
   }
 }
@@ -151,12 +184,18 @@ OI_API int oi_dyt_step(float* h, const float* branch, const void* post_alpha, co
   const int threads = quads >= kDytThreads ? kDytThreads : ((quads + 31) / 32) * 32;
   const dim3 grid(rows, (quads + threads - 1) / threads);
   cudaStream_t s = (cudaStream_t)stream;
-  if (!out || out_dtype == OI_F32)
-    oi_launch(dyt_step_kernel<float>, grid, threads, 0, s, h, branch, post, pre, (float*)out, row_idx, width);
-  else if (out_dtype == OI_BF16)
-    oi_launch(dyt_step_kernel<bf16>, grid, threads, 0, s, h, branch, post, pre, (bf16*)out, row_idx, width);
+  auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const bool vec = width % 4 == 0 && al(h) && al(branch) && al(out) && al(post_w) && al(post_b) && al(pre_w) && al(pre_b);
+#define OI_DYT(T)                                                                                                        \
+  do {                                                                                                                   \
+    if (vec) oi_launch(dyt_step_kernel<T, true>, grid, threads, 0, s, h, branch, post, pre, (T*)out, row_idx, width);    \
+    else oi_launch(dyt_step_kernel<T, false>, grid, threads, 0, s, h, branch, post, pre, (T*)out, row_idx, width);       \
+  } while (0)
+  if (!out || out_dtype == OI_F32) OI_DYT(float);
+  else if (out_dtype == OI_BF16) OI_DYT(bf16);
   else
     OI_REQUIRE(false, "dyt_step: unknown dtype code %d", out_dtype);
+#undef OI_DYT
   OI_CHECK_LAUNCH();
   return OI_OK;
 }

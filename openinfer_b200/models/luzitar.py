@@ -35,8 +35,9 @@ def _position(cfg: LuzitarConfig, rot, interleaved: bool) -> PositionSpec:
 def _mixer(cfg: LuzitarConfig, layer: dict, eps: float):
     W, m = cfg.width, layer["mixer"]
     if layer["type"] == "lightning":
+        decay = m["decay"] if isinstance(m["decay"], (list, tuple)) else [m["decay"]] * int(m["heads"])
         return LinearAttentionSpec(hidden_size=W, num_heads=int(m["heads"]), qk_dim=int(m["dim"]), v_dim=int(m["vdim"]),
-                                   decays=tuple(float(d) for d in m["decay"]), eps=eps)
+                                   decays=tuple(float(d) for d in decay), eps=eps)
     if layer["type"] == "attention":
         dim, vdim = int(m["dim"]), int(m["vdim"])
         mask = m.get("mask") or {}

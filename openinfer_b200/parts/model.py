@@ -164,7 +164,8 @@ class Model:
         if self.spec.embedding_scale != 1.0:
             ops.scale_cap(h, scale=self.spec.embedding_scale)
         if self.embedding_norm is not None:
-            if h.dtype != torch.float32 or not hasattr(self.embedding_norm, "triple"):
+            from .norm import DynamicTanh
+            if h.dtype != torch.float32 or not isinstance(self.embedding_norm, DynamicTanh):
                 raise RuntimeError("the embedding's norm is a dyt norm on a float32 stream")
             ops.dyt_step(h, pre=self.embedding_norm.triple(), out=h)        # in place
         ctx.scratch["model_dtype"] = self.dtype
@@ -446,6 +447,8 @@ class Model:
     def logits(self, h: torch.Tensor, pending: Optional[torch.Tensor], row_idx: torch.Tensor) -> torch.Tensor:
         """Float32 logits [rows, vocab] of the wanted rows only: gather + final norm in one
         kernel, then the head (pegainfer-qwen3/src/prefill.rs:440-477)."""
+        from .block import PendingNormed
+        from .norm import DynamicTanh
         if h.dim() == 3:
             # several streams: the last sublayer's result reaches them, then the wanted rows' streams are summed and normed
             if pending is not None:
@@ -455,10 +458,12 @@ class Model:
             n = self.final_norm
             x = torch.empty((row_idx.numel(), h.shape[2]), dtype=self.dtype, device=h.device)
             ops.hyper_step(h, norm_w=n.weight, eps=n.spec.eps, weight_offset=n.spec.weight_offset, out=x, row_idx=row_idx)
-        elif hasattr(pending, "norm") or hasattr(self.final_norm, "triple"):
+        elif isinstance(self.final_norm, DynamicTanh):
             # a last result that passes a norm of its own on its way into the stream, and a dyt final norm: one kernel forms
             # the wanted rows from stream + norm(result)
             x = torch.empty((row_idx.numel(), h.shape[1]), dtype=self.dtype, device=h.device)
+            if pending is not None and not isinstance(pending, PendingNormed):
+                raise RuntimeError("a dyt final norm follows blocks that hand on a result with its norm, or nothing")
             ops.dyt_step(h, branch=pending.y if pending is not None else None, post=pending.norm.triple() if pending is not None else None,
                          pre=self.final_norm.triple(), out=x, row_idx=row_idx)
         elif h.dtype != self.dtype:
