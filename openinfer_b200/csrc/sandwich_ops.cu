@@ -166,6 +166,102 @@ __global__ void rope_norm_store_kernel(T* __restrict__ qkv, long long row_stride
   for (int d = lane; d < hd; d += 32) dst[d] = from_f32<T>(x[d] * inv);
 }
 
+// The same for heads of 8, 16, 32, 64, 128 or 256 numbers whose rows can be read 16 bytes at a time and whose rotated
+// halves are multiples of eight: eight neighbouring numbers a lane, hd / 8 lanes a head, 256 / hd heads a warp; a number's
+// partner in the rotation comes from the lane rot_half / 8 further on (or back) by shuffles, the sum of squares is reduced
+// over the head's lanes.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rope_norm_store_vec_kernel(T* __restrict__ qkv, long long row_stride, int nq, int nkv, int hd, int qk_dim,
+                           const float* __restrict__ bias_tab, int n_tab, long long tab_stride,
+                           const float* __restrict__ cos_tab, const float* __restrict__ sin_tab, int rot_half, int max_pos,
+                           int unit_norm, float eps, const int* __restrict__ positions, const int* __restrict__ slots,
+                           T* __restrict__ k_cache, T* __restrict__ v_cache, long long page_stride, int page_size, int write_kv,
+                           int tokens) {
+  pdl_start();
+  const int lane = threadIdx.x & 31;
+  const int lph = hd >> 3, per_warp = 32 / lph;               // lanes per head, heads per warp
+  const int sub = lane / lph, l = lane - sub * lph;
+  const int heads_total = write_kv ? nq + 2 * nkv : nq;
+  const long long total = (long long)tokens * heads_total;
+  const long long gw = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  long long item = gw * per_warp + sub;
+  const bool active = item < total;
+  if (!active) item = total - 1;                               // idle lanes follow along (the shuffles want every lane) and store nothing
+  const int token = (int)(item / heads_total), head = (int)(item - (long long)token * heads_total);
+  const int kind = head < nq ? 0 : (head < nq + nkv ? 1 : 2);
+  const int d0 = l * 8;
+  T* src = qkv + (size_t)token * row_stride + (size_t)head * hd + d0;
+  T* dst = src;
+  bool store = active;
+  if (kind != 0) {
+    const int slot = slots[token];
+    store = store && slot >= 0;
+    const int kvh = kind == 1 ? head - nq : head - nq - nkv;
+    if (slot >= 0)
+      dst = (kind == 1 ? k_cache : v_cache) + (size_t)(slot / page_size) * page_stride + (size_t)(slot % page_size) * nkv * hd +
+            (size_t)kvh * hd + d0;
+  }
+  int pos = positions[token];
+  pos = pos < 0 ? 0 : pos;
+  float x[8];
+  if (sizeof(T) == 2) {
+    const uint4 t = *reinterpret_cast<const uint4*>(src);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h2[e]);
+      x[2 * e] = f.x, x[2 * e + 1] = f.y;
+    }
+  } else {
+    const float4 a = reinterpret_cast<const float4*>(src)[0], b = reinterpret_cast<const float4*>(src)[1];
+    x[0] = a.x, x[1] = a.y, x[2] = a.z, x[3] = a.w, x[4] = b.x, x[5] = b.y, x[6] = b.z, x[7] = b.w;
+  }
+  if (bias_tab) {
+    const float4* b4 = reinterpret_cast<const float4*>(bias_tab + (size_t)min(pos, n_tab - 1) * tab_stride + (size_t)head * hd + d0);
+    const float4 a = b4[0], b = b4[1];
+    x[0] += a.x, x[1] += a.y, x[2] += a.z, x[3] += a.w, x[4] += b.x, x[5] += b.y, x[6] += b.z, x[7] += b.w;
+  }
+  // the rotation: numbers [0, rot_half) and [rot_half, 2 rot_half) of q and k heads are partners
+  const bool turns = kind != 2 && d0 < 2 * rot_half;
+  const bool low = d0 < rot_half;
+  const int partner = turns ? (low ? lane + (rot_half >> 3) : lane - (rot_half >> 3)) : lane;
+  float c[8], sn[8];
+  if (turns) {
+    const int p = pos >= max_pos ? max_pos - 1 : pos;
+    const int i0 = low ? d0 : d0 - rot_half;
+    const float4* c4 = reinterpret_cast<const float4*>(cos_tab + (size_t)p * rot_half + i0);
+    const float4* s4 = reinterpret_cast<const float4*>(sin_tab + (size_t)p * rot_half + i0);
+    const float4 ca = c4[0], cb = c4[1], sa = s4[0], sb = s4[1];
+    c[0] = ca.x, c[1] = ca.y, c[2] = ca.z, c[3] = ca.w, c[4] = cb.x, c[5] = cb.y, c[6] = cb.z, c[7] = cb.w;
+    sn[0] = sa.x, sn[1] = sa.y, sn[2] = sa.z, sn[3] = sa.w, sn[4] = sb.x, sn[5] = sb.y, sn[6] = sb.z, sn[7] = sb.w;
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    const float other = __shfl_sync(0xffffffffu, x[e], partner);
+    if (turns) x[e] = low ? x[e] * c[e] - other * sn[e] : x[e] * c[e] + other * sn[e];
+  }
+  float inv = 1.f;
+  if (unit_norm) {
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += d0 + e < qk_dim ? x[e] * x[e] : 0.f;
+    for (int o = lph >> 1; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    if (kind != 2) inv = 1.f / sqrtf(ss / (float)qk_dim + eps);
+  }
+  if (!store) return;
+  if (sizeof(T) == 2) {
+    uint4 t;
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(x[2 * e] * inv, x[2 * e + 1] * inv);
+    *reinterpret_cast<uint4*>(dst) = t;
+  } else {
+    reinterpret_cast<float4*>(dst)[0] = make_float4(x[0] * inv, x[1] * inv, x[2] * inv, x[3] * inv);
+    reinterpret_cast<float4*>(dst)[1] = make_float4(x[4] * inv, x[5] * inv, x[6] * inv, x[7] * inv);
+  }
+}
+
 }  // namespace
 
 // h [*, width] float32 (the stream; updated in place when `branch` is given); branch float32 [rows, width] or null;
@@ -216,6 +312,25 @@ OI_API int oi_rope_norm_store(void* qkv, int dtype, long long row_stride, int to
   const long long warps = (long long)tokens * (write_kv ? nq + 2 * nkv : nq);
   const unsigned blocks = (unsigned)((warps + kRopeWarps - 1) / kRopeWarps);
   cudaStream_t s = (cudaStream_t)stream;
+  auto al = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const int elem = dtype == OI_F32 ? 4 : 2;
+  const bool vec = (hd == 8 || hd == 16 || hd == 32 || hd == 64 || hd == 128 || hd == 256) && rot_half % 8 == 0 && al(qkv) &&
+                   (row_stride * elem) % 16 == 0 && (!bias_tab || (al(bias_tab) && tab_stride % 4 == 0)) &&
+                   (rot_half == 0 || (al(cos_tab) && al(sin_tab))) &&
+                   (!write_kv || (al(k_cache) && al(v_cache) && (page_stride * elem) % 16 == 0)) && (dtype == OI_F32 || dtype == OI_BF16);
+  if (vec) {
+    const int per_warp = 32 / (hd / 8);
+    const long long vwarps = (warps + per_warp - 1) / per_warp;
+    const unsigned vblocks = (unsigned)((vwarps + 3) / 4);
+#define OI_RNSV(T)                                                                                                           \
+  oi_launch(rope_norm_store_vec_kernel<T>, vblocks, 128, 0, s, (T*)qkv, row_stride, nq, nkv, hd, qk_dim, bias_tab, n_tab,     \
+            tab_stride, cos_tab, sin_tab, rot_half, max_pos, unit_norm, eps, positions, slots, (T*)k_cache, (T*)v_cache,      \
+            page_stride, page_size, write_kv, tokens)
+    if (dtype == OI_F32) OI_RNSV(float); else OI_RNSV(bf16);
+#undef OI_RNSV
+    OI_CHECK_LAUNCH();
+    return OI_OK;
+  }
 #define OI_RNS(T)                                                                                                          \
   oi_launch(rope_norm_store_kernel<T>, blocks, kRopeWarps * 32, 0, s, (T*)qkv, row_stride, nq, nkv, hd, qk_dim, bias_tab, n_tab, \
             tab_stride, cos_tab, sin_tab, rot_half, max_pos, unit_norm, eps, positions, slots, (T*)k_cache, (T*)v_cache,    \

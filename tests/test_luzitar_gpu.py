@@ -98,7 +98,9 @@ def test_dynamic_tanh_step_kernel(out_dtype, rows, width):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("nq,nkv,hd,qk,rot_dims,taps,page", [(4, 2, 24, 16, 8, 3, 4), (6, 6, 16, 8, 4, 0, 16), (3, 1, 40, 40, 0, 5, 8),
-                                                               (2, 1, 64, 64, 64, 1, 16), (5, 5, 16, 10, 6, 2, 2)])
+                                                               (2, 1, 64, 64, 64, 1, 16), (5, 5, 16, 10, 6, 2, 2), (4, 2, 128, 128, 64, 4, 16),
+                                                               (6, 2, 32, 24, 16, 3, 8), (2, 2, 256, 200, 128, 2, 16), (3, 1, 8, 8, 0, 2, 4),
+                                                               (1, 1, 16, 16, 16, 0, 16)])
 def test_bias_rotation_unit_norm_and_store_kernel(dtype, nq, nkv, hd, qk, rot_dims, taps, page):
     """One pass over the fused q | k | v rows: the bias by position, the rotation of the first numbers of q and k heads, the
     unit norm over qk numbers behind it, q in place, k and v to their slots; a padding row stores nothing."""
