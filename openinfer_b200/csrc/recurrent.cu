@@ -263,6 +263,35 @@ __global__ void __launch_bounds__(kThreads) recurrent_scan_kernel(ScanArgs a, in
         }
       }
     }
+    if (kMode == kLinearDecay) {
+      // Four rows at a time. The read-out does not feed the state, so the chain from row to row is one multiply-add a
+      // register; the four rows' sums over the lanes of a column are four shuffle trees that do not wait for one another.
+      for (; tt + 3 < n; tt += 4) {
+        float o4[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float* r = stage_now + (size_t)(tt + u) * rec;
+          const float v = vals[(tt + u) * kCols + cl];
+          float k[R], q[R];
+          load_channels<kLanes, R, kVec4>(k, r, D, j);
+          load_channels<kLanes, R, kVec4>(q, r + D, D, j);
+          float num[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int i = 0; i < R; ++i) {
+            C[i] = fmaf(lam, C[i], k[i] * v);
+            num[i & 3] += C[i] * q[i];
+          }
+          o4[u] = (num[0] + num[1]) + (num[2] + num[3]);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) o4[u] = lanes_sum<kLanes>(o4[u]);
+        if (j == 0 && col) {
+          float* o_row = a.out + (size_t)(start + t0 + tt) * a.ld_out + (size_t)h * V + c;
+#pragma unroll
+          for (int u = 0; u < 4; ++u) o_row[(size_t)u * a.ld_out] = o4[u];
+        }
+      }
+    }
 #pragma unroll 2
     for (; tt < n; ++tt) {
       const float* r = stage_now + (size_t)tt * rec;
@@ -356,6 +385,25 @@ __global__ void head_norm_gate_kernel(TO* __restrict__ out, long long ld_out, co
   }
 }
 
+// The same for ONE norm over a whole row of many numbers (H = 1: a norm over all heads together): one block a row.
+template <typename TO>
+__global__ void row_norm_gate_kernel(TO* __restrict__ out, long long ld_out, const float* __restrict__ o, long long ld_o,
+                                     const float* __restrict__ gate, long long ld_gate, const void* __restrict__ w, int w_dtype,
+                                     int V, float eps, float scale) {
+  pdl_start();
+  __shared__ float red[32];
+  const int t = blockIdx.x;
+  const float* row = o + (size_t)t * ld_o;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < V; c += blockDim.x) ss += row[c] * row[c];
+  ss = block_sum(ss, red);
+  const float r = 1.f / sqrtf(ss / (float)V + eps);
+  for (int c = threadIdx.x; c < V; c += blockDim.x) {
+    const float gz = gate[(size_t)t * ld_gate + c];
+    out[(size_t)t * ld_out + c] = from_f32<TO>(row[c] * r * load_as_f32(w, w_dtype, c) * (1.f / (1.f + expf(-gz))) * scale);
+  }
+}
+
 }  // namespace
 
 // floats of scratch the scan wants per row: oi_recurrent_scan's `prep` is [tokens, H, that]
@@ -393,7 +441,9 @@ OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q
   else if (mode == kLinearDecay) oi_launch(recurrent_prepare_kernel<kLinearDecay>, (warps + 3) / 4, 128, 0, s, a);
   else oi_launch(recurrent_prepare_kernel<kGatedDelta>, (warps + 3) / 4, 128, 0, s, a);
   OI_CHECK_LAUNCH();
-  const int chunk = D <= 64 ? 16 : (D <= 128 ? 8 : (D <= 256 ? 4 : 2));   // rows per buffer: two buffers of at most 13 KB
+  // rows per buffer: two buffers of at most 13 KB; the linear decay, which walks four rows at a time, takes more (up to 44 KB)
+  const int chunk = mode == kLinearDecay ? (D <= 64 ? 24 : (D <= 128 ? 12 : (D <= 256 ? 4 : 2)))
+                                         : (D <= 64 ? 16 : (D <= 128 ? 8 : (D <= 256 ? 4 : 2)));
 #define OI_SCAN_AS(MODE, LANES, REGS)                                                                                   \
   do {                                                                                                                  \
     constexpr int cols = kThreads / LANES;                                                                              \
@@ -415,9 +465,17 @@ OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q
     else if (D <= 256) OI_SCAN_AS(MODE, 16, 16);      \
     else OI_SCAN_AS(MODE, 32, 16);                    \
   } while (0)
+  // (the linear decay's sums over a column's lanes are off the chain from row to row: more lanes a column, fewer columns a
+  // block and so more blocks)
   if (mode == kMatrixMemory) OI_SCAN(kMatrixMemory);
-  else if (mode == kLinearDecay) OI_SCAN(kLinearDecay);
-  else OI_SCAN(kGatedDelta);
+  else if (mode == kLinearDecay) {
+    if (D <= 16) OI_SCAN_AS(kLinearDecay, 4, 4);
+    else if (D <= 32) OI_SCAN_AS(kLinearDecay, 8, 4);
+    else if (D <= 64) OI_SCAN_AS(kLinearDecay, 16, 4);
+    else if (D <= 128) OI_SCAN_AS(kLinearDecay, 16, 8);
+    else if (D <= 256) OI_SCAN_AS(kLinearDecay, 32, 8);
+    else OI_SCAN_AS(kLinearDecay, 32, 16);
+  } else OI_SCAN(kGatedDelta);
 #undef OI_SCAN
 #undef OI_SCAN_AS
   OI_CHECK_LAUNCH();
@@ -431,6 +489,15 @@ OI_API int oi_head_norm_gate(void* out, int out_dtype, long long ld_out, const f
   if (tokens == 0) return OI_OK;
   const int warps = tokens * H, blocks = (warps + 7) / 8;
   cudaStream_t s = (cudaStream_t)stream;
+  if (H == 1 && V >= 256 && (out_dtype == OI_F32 || out_dtype == OI_BF16)) {     // one long row: a block a row, not a warp
+    const int threads = V >= 1024 ? 256 : 128;
+    if (out_dtype == OI_F32)
+      oi_launch(row_norm_gate_kernel<float>, tokens, threads, 0, s, (float*)out, ld_out, o, ld_o, gate, ld_gate, w, w_dtype, V, eps, scale);
+    else
+      oi_launch(row_norm_gate_kernel<bf16>, tokens, threads, 0, s, (bf16*)out, ld_out, o, ld_o, gate, ld_gate, w, w_dtype, V, eps, scale);
+    OI_CHECK_LAUNCH();
+    return OI_OK;
+  }
   if (out_dtype == OI_F32)
     oi_launch(head_norm_gate_kernel<float>, blocks, 256, 0, s, (float*)out, ld_out, o, ld_o, gate, ld_gate, w, w_dtype, w_stride, tokens, H, V, eps, scale);
   else if (out_dtype == OI_BF16)

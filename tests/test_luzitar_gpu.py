@@ -257,6 +257,21 @@ def test_linear_attention_scan(H, D, V):
     assert torch.equal(sd[1].cpu(), state[1])
 
 
+@pytest.mark.parametrize("out_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("rows,width", [(1, 24), (9, 256), (3, 1030), (40, 2048)])
+def test_norm_over_all_heads_and_gate(out_dtype, rows, width):
+    """The read-outs of all heads normed together (one weight over the whole row) and gated: short rows by a warp, long rows
+    by a block."""
+    from openinfer_b200.kernels import ops
+    g = torch.Generator().manual_seed(rows + width)
+    o, gate = torch.randn(rows, width + 8, generator=g) * 3, torch.randn(rows, width + 4, generator=g)
+    w = (1 + 0.2 * torch.randn(width, generator=g)).to(torch.bfloat16)
+    out = torch.empty(rows, width, device="cuda", dtype=out_dtype)
+    ops.head_norm_gate(out, _dev(o)[:, :width], _dev(gate)[:, 2: 2 + width], _dev(w), 1, width, 1e-5, weight_per_head=True)
+    ref = plain.rms(o[:, :width].double(), 1e-5, w.double()) * torch.sigmoid(gate[:, 2: 2 + width].double())
+    assert (out.double().cpu() - ref).abs().max().item() < (1e-5 if out_dtype == torch.float32 else 3e-2) * max(1.0, ref.abs().max().item())
+
+
 # ---------------------------------------------------------------------------------------------- mechanisms alone
 def _one_layer(layer, width=48, vocab=83, **kw):
     return model(vocab, width, [layer], **kw)
