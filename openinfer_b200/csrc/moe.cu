@@ -45,18 +45,21 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     if (vec) {       // a lane takes 16 bytes of the row and of each expert's weights at a time
       const T* wt = reinterpret_cast<const T*>(w);
+      // (experts beyond the last read the last one's row again and are not stored: loads without a condition can all be
+      // in flight at once, where a load behind a test waits for the one before it; 21.8 -> see the design notes)
+      const T* wrow[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) wrow[i] = wt + (size_t)min(e0 + i, E - 1) * K;
 #pragma unroll 2
       for (int k = lane * kVec; k < K; k += 32 * kVec) {
-        T xv[kVec];
+        T xv[kVec], wv[4][kVec];
         *reinterpret_cast<uint4*>(xv) = *reinterpret_cast<const uint4*>(xr + k);
 #pragma unroll
-        for (int i = 0; i < 4; ++i)
-          if (e0 + i < E) {
-            T wv[kVec];
-            *reinterpret_cast<uint4*>(wv) = *reinterpret_cast<const uint4*>(wt + (size_t)(e0 + i) * K + k);
+        for (int i = 0; i < 4; ++i) *reinterpret_cast<uint4*>(wv[i]) = *reinterpret_cast<const uint4*>(wrow[i] + k);
 #pragma unroll
-            for (int e = 0; e < kVec; ++e) acc[i] += to_f32(wv[e]) * to_f32(xv[e]);
-          }
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int e = 0; e < kVec; ++e) acc[i] += to_f32(wv[i][e]) * to_f32(xv[e]);
       }
     } else {
 #pragma unroll 4
