@@ -568,36 +568,57 @@ __global__ void __launch_bounds__(128) moe_gemv_kernel(const T* __restrict__ A, 
   __syncthreads();
   const T* We = Wt + (size_t)ids[p] * w_expert_stride;
   const bool vec = K % kVec == 0 && ((uintptr_t)We % 16 == 0);
-  for (int n = blockIdx.y * kRows + wi; n < min(N, (int)(blockIdx.y + 1) * kRows); n += 4) {
+  const int n_end = min(N, (int)(blockIdx.y + 1) * kRows);
+  if (vec) {
+    // two output rows of the warp at a time, two steps along K unrolled: eight 16-byte loads in flight a lane (a row beyond
+    // the block's last reads that one again and is not stored)
+    for (int n = blockIdx.y * kRows + wi; n < n_end; n += 8) {
+      const int n1 = n + 4 < n_end ? n + 4 : n;
+      const T* wg0 = We + (size_t)n * K;
+      const T* wg1 = We + (size_t)n1 * K;
+      const T* wu0 = wg0 + (size_t)N * K;
+      const T* wu1 = wg1 + (size_t)N * K;
+      float g0 = 0.f, u0 = 0.f, g1 = 0.f, u1 = 0.f;
+#pragma unroll 2
+      for (int k = lane * kVec; k < K; k += 32 * kVec) {
+        T a0[kVec], b0[kVec], a1[kVec], b1[kVec];
+        *reinterpret_cast<uint4*>(a0) = *reinterpret_cast<const uint4*>(wg0 + k);
+        *reinterpret_cast<uint4*>(a1) = *reinterpret_cast<const uint4*>(wg1 + k);
+        if (kGlu) {
+          *reinterpret_cast<uint4*>(b0) = *reinterpret_cast<const uint4*>(wu0 + k);
+          *reinterpret_cast<uint4*>(b1) = *reinterpret_cast<const uint4*>(wu1 + k);
+        }
+#pragma unroll
+        for (int e = 0; e < kVec; ++e) {
+          const float xv = xs[k + e];
+          g0 += to_f32(a0[e]) * xv;
+          g1 += to_f32(a1[e]) * xv;
+          if (kGlu) {
+            u0 += to_f32(b0[e]) * xv;
+            u1 += to_f32(b1[e]) * xv;
+          }
+        }
+      }
+      g0 = warp_sum(g0), g1 = warp_sum(g1);
+      if (kGlu) u0 = warp_sum(u0), u1 = warp_sum(u1);
+      if (lane == 0) {
+        out[(size_t)p * ld_out + n] = from_f32<TO>(kGlu ? glu_act<false>(g0, u0, act, limit) : g0);
+        if (n1 != n) out[(size_t)p * ld_out + n1] = from_f32<TO>(kGlu ? glu_act<false>(g1, u1, act, limit) : g1);
+      }
+    }
+    return;
+  }
+  for (int n = blockIdx.y * kRows + wi; n < n_end; n += 4) {
     const T* wg = We + (size_t)n * K;
     const T* wu = We + (size_t)(N + n) * K;
     float g = 0.f, u = 0.f;
-    if (vec) {
-      for (int k = lane * kVec; k < K; k += 32 * kVec) {
-        T a[kVec], b[kVec];
-        *reinterpret_cast<uint4*>(a) = *reinterpret_cast<const uint4*>(wg + k);
-        if (kGlu) *reinterpret_cast<uint4*>(b) = *reinterpret_cast<const uint4*>(wu + k);
-#pragma unroll
-        for (int e = 0; e < kVec; ++e) {
-          g += to_f32(a[e]) * xs[k + e];
-          if (kGlu) u += to_f32(b[e]) * xs[k + e];
-        }
-      }
-    } else {
-      for (int k = lane; k < K; k += 32) {
-        g += to_f32(wg[k]) * xs[k];
-        if (kGlu) u += to_f32(wu[k]) * xs[k];
-      }
+    for (int k = lane; k < K; k += 32) {
+      g += to_f32(wg[k]) * xs[k];
+      if (kGlu) u += to_f32(wu[k]) * xs[k];
     }
     g = warp_sum(g);
     if (kGlu) u = warp_sum(u);
-    if (lane == 0) {
-      float v = g;
-      if (kGlu) {
-        v = glu_act<false>(g, u, act, limit);
-      }
-      out[(size_t)p * ld_out + n] = from_f32<TO>(v);
-    }
+    if (lane == 0) out[(size_t)p * ld_out + n] = from_f32<TO>(kGlu ? glu_act<false>(g, u, act, limit) : g);
   }
 }
 
