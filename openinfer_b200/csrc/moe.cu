@@ -46,7 +46,7 @@ __global__ void moe_router_kernel(const T* __restrict__ x, long long ldx, const 
     if (vec) {       // a lane takes 16 bytes of the row and of each expert's weights at a time
       const T* wt = reinterpret_cast<const T*>(w);
       // (experts beyond the last read the last one's row again and are not stored: loads without a condition can all be
-      // in flight at once, where a load behind a test waits for the one before it; 21.8 -> see the design notes)
+      // in flight at once, where a load behind a test waits for the one before it: 8 rows of width 2,048 21.8 -> 8.2 us)
       const T* wrow[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) wrow[i] = wt + (size_t)min(e0 + i, E - 1) * K;
