@@ -494,7 +494,7 @@ def luzitar_configs(key, layers=None):
     unit norm behind the rotation, a window that keeps the first 64 keys) and two "latent_attention" (a latent of 96 numbers
     and a rotated key part of 32 in one cached row of 128; the second reads the first one's cache); every layer has sixteen
     experts of a quarter of Qwen3's feed-forward in four groups of which the two best are open, two experts a token. Qwen3 as
-    in ``design_configs``."""
+    in ``design_configs``; the third configuration returned is Bubalix at the same sizes."""
     width, n_layers, heads, window, _, inter = DESIGN_SIZES[key]
     n_layers = layers or n_layers
     lin_heads = max(1, heads // 2)
@@ -511,7 +511,8 @@ def luzitar_configs(key, layers=None):
             m["kv_from"] = i - 1
         lay.append({"type": kind, "mixer": m, "mlp": dict(mlp)})
     luzitar = {"architecture": "Luzitar", "vocab": DESIGN_VOCAB, "width": width, "norm": {"eps": 1e-6}, "logit_softcap": 30.0, "layers": lay}
-    return luzitar, design_configs(key, layers)[1]
+    # beside Qwen3 also the engine's closest design (experts in every layer, filtered attention, latent attention) at equal sizes
+    return luzitar, design_configs(key, layers)[1], bubalix_configs(key, layers)[0]
 
 
 def _part_tensors(torch, part, seen=None):
@@ -693,7 +694,7 @@ def design_mode(args, torch, mods, peaks, peaks_src):
                 raise SystemExit(f"--design-sizes: unknown size {key!r} (known: {', '.join(DESIGN_SIZES)})")
             rec = {"width": DESIGN_SIZES[key][0], "layers": args.layers or DESIGN_SIZES[key][1]}
             configs = {"pilonex": pilonex_configs, "bubalix": bubalix_configs, "luzitar": luzitar_configs}.get(args.design, design_configs)(key, args.layers)
-            for arch, cfg in zip((args.design, "qwen3"), configs):
+            for arch, cfg in zip((args.design, "qwen3", "bubalix"), configs):      # (a third entry only where the design names one)
                 b = DesignBench(torch, mods, cfg, args.dtype, CONTEXT, 64, steps + warm + 16)
                 r = {"weights_gb": round(b.runner.model.weight_bytes() / 1e9, 3)}
                 for batch in (1, 8, 64):
